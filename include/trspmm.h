@@ -1,0 +1,144 @@
+/*
+ * trspmm.h — C ABI of libtrspmm.so: the hybrid sparse hot path (format builder, fused
+ * TC-block / 2:4 mma.sp / CSR-remainder SpMM, SDDMM) as hand-written CUDA for sm_100a.
+ *
+ * Conventions
+ *   - every entry point returns 0 on success, a negative TRS_E_* value for an argument error
+ *     found on the host before anything was launched, or a positive cudaError_t value;
+ *   - no exception crosses this boundary; trs_strerror() explains any returned code;
+ *   - pointers are plain device pointers unless the name says "host"; sizes are element counts;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - there is no CPU fallback: without a CUDA device every compute entry returns an error.
+ *
+ * The file:line citations name the interface of the reference project each entry replaces.
+ */
+#ifndef TRSPMM_H_
+#define TRSPMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRS_OK 0
+#define TRS_E_ARG (-1)        /* null pointer / non-positive size / unsupported value          */
+#define TRS_E_WINDOW (-2)     /* window outside 1..16 (mGCN_online.cpp:888, block_online.cpp:553) */
+#define TRS_E_OFFSETS (-3)    /* a prefix array is not monotone or does not start at 0          */
+#define TRS_E_SHAPE (-4)      /* array lengths inconsistent with each other                     */
+#define TRS_E_COLUMN (-5)     /* a column id outside [-1, kOri)                                 */
+#define TRS_E_ROW (-6)        /* a row id outside [0, mOri)                                     */
+#define TRS_E_WORKSPACE (-7)  /* caller-provided workspace too small                            */
+#define TRS_E_NOT_CANONICAL (-8) /* CSR columns not ascending / duplicated inside a row         */
+#define TRS_E_NO_DEVICE (-9)  /* no usable CUDA device                                          */
+#define TRS_E_LIMIT (-10)     /* size beyond a documented fixed limit                           */
+
+#define TRS_OUT_F32 0 /* what the reference returns (mGCN_online.cpp:934) */
+#define TRS_OUT_F16 1
+
+typedef uint16_t trs_half; /* IEEE binary16 bits */
+
+/* The arrays block_sptc_2to4_online returns (block_online.cpp:844-870) that the forward pass
+ * consumes (mGCN_online.cpp:760-800), with the value arrays already cast to fp16 as
+ * mdataset2_online.py:151-153 does.  All pointers live in the same memory space. */
+typedef struct trs_format {
+    /* dense 16x8 tensor-core blocks */
+    const int32_t* t_row_offset;   /* [parts_t + 1]  prefix of blocks per part               */
+    const int32_t* t_block_offset; /* [blocks + 1]   prefix of values per block              */
+    const int32_t* t_column;       /* [blocks * 8]   column per slot, -1 padded              */
+    const trs_half* t_value;       /* [tc_nnz]                                               */
+    const int32_t* t_window_row;   /* [parts_t]      first global row of the part's window   */
+    const int64_t* t_binary;       /* [blocks * 2]   occupancy bitmaps rows 0-7 / 8-15       */
+    int32_t parts_t;
+    int32_t blocks;
+    /* CUDA-core CSR remainder: long parts, then short parts */
+    const int32_t* c_row_offset;   /* [parts_c + 1] */
+    const int32_t* c_row;          /* [parts_c]     */
+    const int32_t* c_column;
+    const trs_half* c_value;
+    int32_t parts_c;
+    const int32_t* cs_row_offset;  /* [parts_c_short + 1] */
+    const int32_t* cs_row;
+    const int32_t* cs_column;
+    const trs_half* cs_value;
+    int32_t parts_c_short;
+    /* packed 2:4 tiles for mma.sp m16n8k16 */
+    const int32_t* s_window_tile_offset; /* [num_windows + 1] */
+    const int32_t* s_tile_column;        /* [tiles * 16]      */
+    const uint32_t* s_packed_a;          /* [tiles * 64]      */
+    const uint32_t* s_packed_meta;       /* [tiles * 8]       */
+    int32_t num_windows;
+    int32_t tiles;
+} trs_format;
+
+typedef struct trs_spmm_plan trs_spmm_plan; /* opaque */
+
+/* Per-call timings in milliseconds (device time, CUDA events), the slots of the reference's
+ * return tuple [C, ms, ms_tc, ms_cuda_long, ms_cuda_short, ms_sptc] (mGCN_online.cpp:1130-1137).
+ * The three routes run fused in one kernel here, so only `total` is a measurement. */
+typedef struct trs_timing {
+    float total_ms;
+    float tc_ms, cuda_long_ms, cuda_short_ms, sptc_ms; /* always 0: fused */
+    float h2d_ms, d2h_ms;
+} trs_timing;
+
+const char* trs_strerror(int code);
+int trs_version(void);
+int trs_device_count(void);
+
+/* ---- SpMM: plan over device-resident format arrays ---------------------------------------
+ * Replaces the device half of spmm_forward_fp16_tcu_cuda_sptc_mma_parallel_online
+ * (mGCN_online.cpp:760-1138 -> mGCNkernel_online.cu:1529-1727).  The plan validates the
+ * arrays on the device (monotone prefixes, column / row ranges), derives per-window work
+ * items and keeps only small index arrays of its own; the format arrays stay caller-owned and
+ * must outlive the plan.  `validate` = 0 skips the range checks. */
+int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, int k_cols, int window,
+                         int validate, void* stream, trs_spmm_plan** out_plan);
+int trs_spmm_plan_destroy(trs_spmm_plan* plan);
+/* Scratch the run needs for feature width F (partial sums of windows split across CTAs). */
+int trs_spmm_workspace_bytes(const trs_spmm_plan* plan, int F, size_t* bytes);
+/* C[m_rows, F] = A' * B[k_cols, F]; fp16 inputs, fp32 accumulate; C fully written (no memset
+ * needed), fp32 or fp16 per out_dtype.  Asynchronous on `stream`; allocates nothing. */
+int trs_spmm_run(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
+                 void* workspace, size_t workspace_bytes, void* stream);
+/* Number of kernels one trs_spmm_run launches (1, or 2 when some window is split). */
+int trs_spmm_launches(const trs_spmm_plan* plan);
+
+/* ---- SpMM with HOST buffers: the reference's calling convention ------------------------------
+ * trs_spmm_forward_host mirrors spmm_forward_fp16_tcu_cuda_sptc_mma_parallel_online
+ * (mGCN_online.cpp:760-800): every array is a host pointer, device memory is allocated,
+ * filled, used `epoches` times and released inside the call, C is fp32 [mOri, dimN] on the host.
+ * The compat entries with SPTC-only inputs (forward_fp16_sptc_mma_packed_online,
+ * mGCN_online.cpp:654-757) are the same call with the other array groups empty. */
+int trs_spmm_forward_host(const trs_format* host_format, const trs_half* rhs_host, float* out_host,
+                          int dimN, int mOri, int kOri, int window, int epoches, trs_timing* timing);
+
+/* Resident-format variant for host callers: the format is uploaded once into a handle; each
+ * call copies B host->device, runs, and copies C device->host. */
+typedef struct trs_resident trs_resident;
+int trs_resident_create(const trs_format* host_format, int mOri, int kOri, int window,
+                        int max_dimN, trs_resident** out);
+int trs_resident_forward(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN,
+                         int out_dtype, trs_timing* timing);
+int trs_resident_destroy(trs_resident* h);
+
+/* ---- un-packed SPTC arrays -> SpMM (compat) -------------------------------------------------
+ * forward_fp16_sptc_online / forward_fp16_sptc_mma_online (mGCN_online.cpp:202-400, 404-652)
+ * take s_column[G,4], s_value[G,window,2] fp32, s_pos[G,window,2] i8 and a per-group window
+ * (or per-window offsets).  Host pointers; C fp32 on the host. */
+int trs_sptc_unpacked_forward_host(const int32_t* s_column, const float* s_value, const int8_t* s_pos,
+                                   const int32_t* s_window, const int32_t* s_offsets, int groups,
+                                   int num_windows, const trs_half* rhs_host, float* out_host,
+                                   int window, int dimN, int mOri, int kOri, int epoches,
+                                   trs_timing* timing);
+
+/* ---- SDDMM (no counterpart in the reference; defined by BASELINE config 3) -----------------
+ * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e. */
+int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y,
+              trs_half* out, int n_rows, int n_cols, int K, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRSPMM_H_ */

@@ -1,0 +1,179 @@
+"""GPU parity of the fused SpMM against the CPU oracle, through the C ABI.
+
+Tolerances (north-star contract): fp16 output max relative error <= 1e-2 and mean relative
+error <= 1e-3 against the fp32 evaluation of what the format arrays encode; fp32 output within
+2e-4 max relative error (fp16 inputs, fp32 accumulation, different summation order).
+"""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from trspmm import Format, SpmmPlan, graphs
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).parent / "golden"
+CASES = json.loads((GOLD / "cases.json").read_text())
+
+MAX_REL_F16, MEAN_REL_F16 = 1e-2, 1e-3
+MAX_REL_F32 = 2e-4
+
+
+def _golden(name):
+    z = np.load(GOLD / f"{name}.npz")
+    arrays = [torch.from_numpy(z[n]) for n in O.FORMAT_NAMES]
+    return arrays, int(z["in_rowptr"].shape[0] - 1)
+
+
+def _check(out_f32, out_f16, ref):
+    mx, mean = O.rel_errors(out_f32.cpu(), ref)
+    assert mx <= MAX_REL_F32, f"fp32 output max rel {mx}"
+    mx, mean = O.rel_errors(out_f16.cpu(), ref)
+    assert mx <= MAX_REL_F16 and mean <= MEAN_REL_F16, f"fp16 output max rel {mx} mean rel {mean}"
+
+
+@pytest.mark.parametrize("name", sorted(CASES["small"]))
+@pytest.mark.parametrize("F", [32, 64, 128])
+def test_spmm_matches_oracle_on_golden_formats(name, F):
+    arrays, n = _golden(name)
+    torch.manual_seed(1)
+    B = torch.randn(n, F).half()
+    ref = O.spmm_from_format(arrays, B, n)
+    fmt = Format(arrays).to("cuda")
+    plan = SpmmPlan(fmt, n, n)
+    Bd = B.cuda()
+    _check(plan.run(Bd, out_dtype=torch.float32), plan.run(Bd, out_dtype=torch.float16), ref)
+
+
+@pytest.mark.parametrize("F", [8, 40, 100, 104, 256, 264, 3, 33])
+def test_spmm_feature_widths(F):
+    arrays, n = _golden("clustered_n512")
+    torch.manual_seed(2)
+    B = torch.randn(n, F).half()
+    ref = O.spmm_from_format(arrays, B, n)
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    _check(plan.run(B.cuda(), out_dtype=torch.float32), plan.run(B.cuda(), out_dtype=torch.float16), ref)
+
+
+def test_spmm_route_isolation():
+    """Each route alone (the other arrays emptied) reproduces that route's share of the product."""
+    arrays, n = _golden("rmat_s9_minnnz")
+    named = dict(zip(O.FORMAT_NAMES, arrays))
+    torch.manual_seed(3)
+    B = torch.randn(n, 64).half()
+    groups = {
+        "tc": ["t_row_offset", "t_block_offset", "t_column", "t_value", "t_window_row", "t_atomic", "t_binary"],
+        "csr": ["c_row_offset", "c_row", "c_atomic", "c_column", "c_value",
+                "cs_row_offset", "cs_row", "cs_atomic", "cs_column", "cs_value"],
+        "sptc": ["s_column", "s_mask", "s_value", "s_pos", "s_window", "s_tile_window", "s_tile_group",
+                 "s_tile_column", "s_packed_a", "s_packed_meta"],
+    }
+    total = torch.zeros(n, 64)
+    for keep in groups:
+        sub = {}
+        for k, v in named.items():
+            drop = any(k in g for r, g in groups.items() if r != keep)
+            sub[k] = v[:0].clone() if drop else v
+        if keep != "sptc":
+            sub["s_offset"] = torch.zeros_like(named["s_offset"])
+            sub["s_window_tile_offset"] = torch.zeros_like(named["s_window_tile_offset"])
+        else:
+            sub["s_offset"] = named["s_offset"]
+            sub["s_window_tile_offset"] = named["s_window_tile_offset"]
+        ref = O.spmm_from_format(sub, B, n)
+        got = SpmmPlan(Format(sub).to("cuda"), n, n).run(B.cuda(), out_dtype=torch.float32).cpu()
+        mx, _ = O.rel_errors(got, ref)
+        assert mx <= MAX_REL_F32, (keep, mx)
+        total += got
+    mx, _ = O.rel_errors(total, O.spmm_from_format(named, B, n))
+    assert mx <= 5e-4
+
+
+def test_spmm_split_windows_are_deterministic(monkeypatch):
+    """Windows cut into several work items (partial sums + fixed-order reduction) give the same
+    bits on every run and the same numbers as the unsplit schedule."""
+    rp, col, val = graphs.rmat_graph(11, 16, seed=5)
+    n = rp.numel() - 1
+    arrays, _ = O.build_format(rp, col, val)
+    B = torch.randn(n, 128, generator=torch.Generator().manual_seed(0)).half()
+    ref = O.spmm_from_format(arrays, B, n)
+    fmt = Format(arrays).to("cuda")
+    base = SpmmPlan(fmt, n, n).run(B.cuda(), out_dtype=torch.float32)
+    monkeypatch.setenv("TRS_CHUNK_STEPS", "8")
+    plan = SpmmPlan(fmt, n, n)
+    assert plan.launches == 2 and plan.workspace_bytes(128) > 0
+    a = plan.run(B.cuda(), out_dtype=torch.float32)
+    b = plan.run(B.cuda(), out_dtype=torch.float32)
+    assert torch.equal(a, b)
+    assert O.rel_errors(a.cpu(), ref)[0] <= MAX_REL_F32
+    assert O.rel_errors(a.cpu(), base.cpu())[0] <= 1e-5
+    h = plan.run(B.cuda(), out_dtype=torch.float16)
+    mx, mean = O.rel_errors(h.cpu(), ref)
+    assert mx <= MAX_REL_F16 and mean <= MEAN_REL_F16
+
+
+def test_spmm_config0_uniform_vs_torch_sparse():
+    """BASELINE config 0: uniform N=4096, F=64.  Checked against the arrays' own meaning (L1) and,
+    on rows without dropped entries, against torch.sparse CSR A.B (L2)."""
+    rp, col, val = graphs.uniform_graph(4096, 16, 0)
+    n = 4096
+    arrays, info = O.build_format(rp, col, val)
+    B = torch.randn(n, 64, generator=torch.Generator().manual_seed(0)).half()
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    out32 = plan.run(B.cuda(), out_dtype=torch.float32).cpu()
+    out16 = plan.run(B.cuda(), out_dtype=torch.float16).cpu()
+    l1 = O.spmm_from_format(arrays, B, n)
+    _check(out32, out16, l1)
+    # rows touched by a dropped entry: mask bit set without a stored slot
+    named = dict(zip(O.FORMAT_NAMES, arrays))
+    cnt_mask = torch.from_numpy(np.unpackbits(named["s_mask"].numpy()[..., None], axis=-1).sum(-1))  # [G,16]
+    cnt_slot = (named["s_pos"] >= 0).sum(-1)
+    bad_g, bad_r = torch.nonzero(cnt_mask > cnt_slot, as_tuple=True)
+    bad_rows = torch.unique(named["s_window"][bad_g].long() * 16 + bad_r)
+    assert int((cnt_mask - cnt_slot).sum()) == info["dropped_nnz"]
+    good = torch.ones(n, dtype=torch.bool)
+    good[bad_rows] = False
+    l2 = O.spmm_csr(rp, col, val, B)
+    assert O.rel_errors(out32[good], l2[good])[0] <= MAX_REL_F32
+    if len(bad_rows):
+        assert O.rel_errors(out32[~good], l2[~good])[0] > MAX_REL_F32  # the drops are real
+
+
+def test_spmm_rejects_bad_arrays():
+    from trspmm import TrsError
+    arrays, n = _golden("clustered_n512")
+    named = dict(zip(O.FORMAT_NAMES, arrays))
+    bad = dict(named); bad["s_tile_column"] = named["s_tile_column"].clone(); bad["s_tile_column"][0, 0] = n + 5
+    with pytest.raises(TrsError) as e:
+        SpmmPlan(Format(bad).to("cuda"), n, n)
+    assert e.value.code == -5
+    bad = dict(named); bad["s_window_tile_offset"] = named["s_window_tile_offset"].clone(); bad["s_window_tile_offset"][3] = 10 ** 6
+    with pytest.raises(TrsError) as e:
+        SpmmPlan(Format(bad).to("cuda"), n, n)
+    assert e.value.code == -3
+    bad = dict(named); bad["cs_row"] = named["cs_row"].clone(); bad["cs_row"][-1] = n
+    with pytest.raises(TrsError) as e:
+        SpmmPlan(Format(bad).to("cuda"), n, n)
+    assert e.value.code == -6
+    with pytest.raises(TrsError) as e:
+        SpmmPlan(Format(named).to("cuda"), n, n, window=17)
+    assert e.value.code == -2
+
+
+def test_ragged_last_window_and_empty_rows():
+    arrays, n = _golden("uniform_n250_ragged")  # 250 rows: last window has 10
+    B = torch.randn(n, 32, generator=torch.Generator().manual_seed(4)).half()
+    ref = O.spmm_from_format(arrays, B, n)
+    out = SpmmPlan(Format(arrays).to("cuda"), n, n).run(B.cuda(), out_dtype=torch.float32)
+    assert out.shape == (250, 32)
+    assert O.rel_errors(out.cpu(), ref)[0] <= MAX_REL_F32
+    # an all-empty matrix still writes zeros everywhere (C needs no memset)
+    rp = torch.zeros(65, dtype=torch.int32)
+    empty, _ = O.build_format(rp, torch.zeros(0, dtype=torch.int32), torch.zeros(0))
+    plan = SpmmPlan(Format(empty).to("cuda"), 64, 64)
+    dst = torch.full((64, 16), 7.0, device="cuda")
+    plan.run(torch.randn(64, 16).half().cuda(), out=dst)
+    assert float(dst.abs().max()) == 0.0

@@ -1,0 +1,331 @@
+// Host-buffer entry points of the C ABI: the reference's calling convention (CPU arrays in,
+// CPU result out; mGCN_online.cpp:760-1138) on top of the device-resident plan API.
+#include <string.h>
+
+#include <vector>
+
+#include "trs_common.cuh"
+
+using namespace trs;
+
+extern "C" const char* trs_strerror(int code) {
+    switch (code) {
+        case TRS_OK: return "ok";
+        case TRS_E_ARG: return "invalid argument (null pointer, non-positive size or unsupported value)";
+        case TRS_E_WINDOW: return "window must be in 1..16 (and exactly 16 when dense TC blocks are present)";
+        case TRS_E_OFFSETS: return "a prefix/offset array is not monotone or does not start at 0";
+        case TRS_E_SHAPE: return "array lengths are inconsistent with each other";
+        case TRS_E_COLUMN: return "a column id lies outside [-1, kOri)";
+        case TRS_E_ROW: return "a row id lies outside [0, mOri)";
+        case TRS_E_WORKSPACE: return "workspace missing or too small";
+        case TRS_E_NOT_CANONICAL: return "CSR input is not canonical (columns must ascend without duplicates in a row)";
+        case TRS_E_NO_DEVICE: return "no usable CUDA device (this library has no CPU fallback)";
+        case TRS_E_LIMIT: return "size exceeds a fixed limit of this entry point";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "unknown error";
+}
+
+extern "C" int trs_version(void) { return 100; }
+
+extern "C" int trs_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+
+namespace {
+
+// Owns the device copies made for one host-format upload.
+struct Upload {
+    std::vector<void*> ptrs;
+    ~Upload() { for (void* p : ptrs) cudaFree(p); }
+    template <class T>
+    int put(const T* host, size_t n, const T** dev) {
+        *dev = nullptr;
+        if (n == 0) return 0;
+        if (!host) return TRS_E_ARG;
+        void* d = nullptr;
+        cudaError_t e = cudaMalloc(&d, n * sizeof(T));
+        if (e != cudaSuccess) return (int)e;
+        ptrs.push_back(d);
+        e = cudaMemcpy(d, host, n * sizeof(T), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) return (int)e;
+        *dev = (const T*)d;
+        return 0;
+    }
+    template <class T>
+    int raw(size_t n, T** dev) {
+        *dev = nullptr;
+        if (n == 0) return 0;
+        void* d = nullptr;
+        cudaError_t e = cudaMalloc(&d, n * sizeof(T));
+        if (e != cudaSuccess) return (int)e;
+        ptrs.push_back(d);
+        *dev = (T*)d;
+        return 0;
+    }
+};
+
+// Host-side checks that need no device (the reference's TORCH_CHECKs, mGCN_online.cpp:888-932)
+// and that make the array lengths below trustworthy.
+int host_lengths(const trs_format& h, size_t* tc_nnz, size_t* c_nnz, size_t* cs_nnz) {
+    *tc_nnz = *c_nnz = *cs_nnz = 0;
+    if (h.parts_t < 0 || h.blocks < 0 || h.parts_c < 0 || h.parts_c_short < 0 || h.num_windows < 0 || h.tiles < 0)
+        return TRS_E_ARG;
+    if (h.parts_t > 0) {
+        if (!h.t_row_offset || !h.t_block_offset) return TRS_E_ARG;
+        if (h.t_row_offset[0] != 0 || h.t_block_offset[0] != 0) return TRS_E_OFFSETS;
+        if (h.t_row_offset[h.parts_t] != h.blocks) return TRS_E_SHAPE;
+        if (h.t_block_offset[h.blocks] < 0) return TRS_E_OFFSETS;
+        *tc_nnz = (size_t)h.t_block_offset[h.blocks];
+    } else if (h.blocks != 0) return TRS_E_SHAPE;
+    if (h.parts_c > 0) {
+        if (!h.c_row_offset) return TRS_E_ARG;
+        if (h.c_row_offset[0] != 0 || h.c_row_offset[h.parts_c] < 0) return TRS_E_OFFSETS;
+        *c_nnz = (size_t)h.c_row_offset[h.parts_c];
+    }
+    if (h.parts_c_short > 0) {
+        if (!h.cs_row_offset) return TRS_E_ARG;
+        if (h.cs_row_offset[0] != 0 || h.cs_row_offset[h.parts_c_short] < 0) return TRS_E_OFFSETS;
+        *cs_nnz = (size_t)h.cs_row_offset[h.parts_c_short];
+    }
+    if (h.num_windows > 0) {
+        if (!h.s_window_tile_offset) return TRS_E_ARG;
+        if (h.s_window_tile_offset[0] != 0) return TRS_E_OFFSETS;
+        if (h.s_window_tile_offset[h.num_windows] != h.tiles) return TRS_E_SHAPE;
+    } else if (h.tiles != 0) return TRS_E_SHAPE;
+    return TRS_OK;
+}
+
+int upload_format(const trs_format& h, Upload& up, trs_format* d) {
+    size_t tc_nnz, c_nnz, cs_nnz;
+    int rc = host_lengths(h, &tc_nnz, &c_nnz, &cs_nnz);
+    if (rc) return rc;
+    *d = h;
+    const bool tc = h.parts_t > 0;
+    if ((rc = up.put(h.t_row_offset, tc ? (size_t)h.parts_t + 1 : 0, &d->t_row_offset))) return rc;
+    if ((rc = up.put(h.t_block_offset, tc ? (size_t)h.blocks + 1 : 0, &d->t_block_offset))) return rc;
+    if ((rc = up.put(h.t_column, tc ? (size_t)h.blocks * 8 : 0, &d->t_column))) return rc;
+    if ((rc = up.put(h.t_value, tc ? tc_nnz : 0, &d->t_value))) return rc;
+    if ((rc = up.put(h.t_window_row, tc ? (size_t)h.parts_t : 0, &d->t_window_row))) return rc;
+    if ((rc = up.put(h.t_binary, tc ? (size_t)h.blocks * 2 : 0, &d->t_binary))) return rc;
+    const bool c = h.parts_c > 0;
+    if ((rc = up.put(h.c_row_offset, c ? (size_t)h.parts_c + 1 : 0, &d->c_row_offset))) return rc;
+    if ((rc = up.put(h.c_row, c ? (size_t)h.parts_c : 0, &d->c_row))) return rc;
+    if ((rc = up.put(h.c_column, c_nnz, &d->c_column))) return rc;
+    if ((rc = up.put(h.c_value, c_nnz, &d->c_value))) return rc;
+    const bool cs = h.parts_c_short > 0;
+    if ((rc = up.put(h.cs_row_offset, cs ? (size_t)h.parts_c_short + 1 : 0, &d->cs_row_offset))) return rc;
+    if ((rc = up.put(h.cs_row, cs ? (size_t)h.parts_c_short : 0, &d->cs_row))) return rc;
+    if ((rc = up.put(h.cs_column, cs_nnz, &d->cs_column))) return rc;
+    if ((rc = up.put(h.cs_value, cs_nnz, &d->cs_value))) return rc;
+    const bool s = h.num_windows > 0;
+    if ((rc = up.put(h.s_window_tile_offset, s ? (size_t)h.num_windows + 1 : 0, &d->s_window_tile_offset))) return rc;
+    if ((rc = up.put(h.s_tile_column, (size_t)h.tiles * 16, &d->s_tile_column))) return rc;
+    if ((rc = up.put(h.s_packed_a, (size_t)h.tiles * 64, &d->s_packed_a))) return rc;
+    if ((rc = up.put(h.s_packed_meta, (size_t)h.tiles * 8, &d->s_packed_meta))) return rc;
+    return TRS_OK;
+}
+
+struct EventPair {
+    cudaEvent_t a = nullptr, b = nullptr;
+    int init() {
+        TRS_CUDA(cudaEventCreate(&a));
+        TRS_CUDA(cudaEventCreate(&b));
+        return 0;
+    }
+    ~EventPair() {
+        if (a) cudaEventDestroy(a);
+        if (b) cudaEventDestroy(b);
+    }
+    float ms() {
+        float m = 0.f;
+        cudaEventElapsedTime(&m, a, b);
+        return m;
+    }
+};
+
+}  // namespace
+
+struct trs_resident {
+    Upload up;
+    trs_format dev;
+    trs_spmm_plan* plan = nullptr;
+    trs_half* d_rhs = nullptr;
+    void* d_out = nullptr;
+    void* d_ws = nullptr;
+    size_t ws_bytes = 0;
+    int m_rows = 0, k_cols = 0, max_dim = 0;
+    cudaStream_t stream = nullptr;
+};
+
+extern "C" int trs_resident_create(const trs_format* host_format, int mOri, int kOri, int window, int max_dimN,
+                                   trs_resident** out) {
+    if (!host_format || !out || max_dimN <= 0) return TRS_E_ARG;
+    *out = nullptr;
+    if (mOri <= 0 || kOri <= 0) return TRS_E_ARG;
+    if (window <= 0 || window > 16) return TRS_E_WINDOW;
+    if (trs_device_count() == 0) return TRS_E_NO_DEVICE;
+    trs_resident* h = new trs_resident();
+    int rc = upload_format(*host_format, h->up, &h->dev);
+    if (!rc) rc = trs_spmm_plan_create(&h->dev, mOri, kOri, window, 1, nullptr, &h->plan);
+    if (!rc) rc = trs_spmm_workspace_bytes(h->plan, max_dimN, &h->ws_bytes);
+    if (!rc) rc = h->up.raw<unsigned char>(h->ws_bytes, (unsigned char**)&h->d_ws);
+    if (!rc) rc = h->up.raw<trs_half>((size_t)kOri * max_dimN, &h->d_rhs);
+    if (!rc) rc = h->up.raw<unsigned char>((size_t)mOri * max_dimN * sizeof(float), (unsigned char**)&h->d_out);
+    if (!rc) {
+        cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) rc = (int)e;
+    }
+    if (rc) { trs_resident_destroy(h); return rc; }
+    h->m_rows = mOri; h->k_cols = kOri; h->max_dim = max_dimN;
+    *out = h;
+    return TRS_OK;
+}
+
+extern "C" int trs_resident_destroy(trs_resident* h) {
+    if (!h) return TRS_OK;
+    if (h->plan) trs_spmm_plan_destroy(h->plan);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return TRS_OK;
+}
+
+extern "C" int trs_resident_forward(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN, int out_dtype,
+                                    trs_timing* timing) {
+    if (!h || !rhs_host || !out_host || dimN <= 0 || dimN > h->max_dim) return TRS_E_ARG;
+    if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
+    const size_t out_bytes = (size_t)h->m_rows * dimN * (out_dtype == TRS_OUT_F16 ? 2 : 4);
+    EventPair ev_in, ev_k, ev_out;
+    if (timing) {
+        memset(timing, 0, sizeof(*timing));
+        int rc = ev_in.init(); if (!rc) rc = ev_k.init(); if (!rc) rc = ev_out.init();
+        if (rc) return rc;
+        cudaEventRecord(ev_in.a, h->stream);
+    }
+    TRS_CUDA(cudaMemcpyAsync(h->d_rhs, rhs_host, (size_t)h->k_cols * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->stream));
+    if (timing) { cudaEventRecord(ev_in.b, h->stream); cudaEventRecord(ev_k.a, h->stream); }
+    int rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, out_dtype, h->d_ws, h->ws_bytes, h->stream);
+    if (rc) return rc;
+    if (timing) { cudaEventRecord(ev_k.b, h->stream); cudaEventRecord(ev_out.a, h->stream); }
+    TRS_CUDA(cudaMemcpyAsync(out_host, h->d_out, out_bytes, cudaMemcpyDeviceToHost, h->stream));
+    if (timing) cudaEventRecord(ev_out.b, h->stream);
+    TRS_CUDA(cudaStreamSynchronize(h->stream));
+    if (timing) {
+        timing->h2d_ms = ev_in.ms();
+        timing->total_ms = ev_k.ms();
+        timing->d2h_ms = ev_out.ms();
+    }
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_forward_host(const trs_format* host_format, const trs_half* rhs_host, float* out_host, int dimN,
+                                     int mOri, int kOri, int window, int epoches, trs_timing* timing) {
+    if (!host_format || !rhs_host || !out_host) return TRS_E_ARG;
+    if (dimN <= 0 || mOri <= 0 || kOri <= 0 || epoches <= 0) return TRS_E_ARG;
+    if (window <= 0 || window > 16) return TRS_E_WINDOW;
+    trs_resident* h = nullptr;
+    int rc = trs_resident_create(host_format, mOri, kOri, window, dimN, &h);
+    if (rc) return rc;
+    trs_timing t1;
+    memset(&t1, 0, sizeof(t1));
+    EventPair ev;
+    rc = ev.init();
+    if (!rc) {
+        cudaError_t e = cudaMemcpyAsync(h->d_rhs, rhs_host, (size_t)kOri * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->stream);
+        if (e != cudaSuccess) rc = (int)e;
+    }
+    // one untimed run, then `epoches` timed ones (mGCNkernel_online.cu:1604-1687 warms up and
+    // averages over epoches the same way); C is fully rewritten by every run
+    if (!rc) rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
+    if (!rc) {
+        cudaEventRecord(ev.a, h->stream);
+        for (int i = 0; i < epoches && !rc; ++i)
+            rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
+        cudaEventRecord(ev.b, h->stream);
+    }
+    if (!rc) {
+        cudaError_t e = cudaMemcpyAsync(out_host, h->d_out, (size_t)mOri * dimN * sizeof(float), cudaMemcpyDeviceToHost, h->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+        if (e != cudaSuccess) rc = (int)e;
+    }
+    if (!rc && timing) {
+        memset(timing, 0, sizeof(*timing));
+        timing->total_ms = ev.ms() / (float)epoches;
+    }
+    trs_resident_destroy(h);
+    return rc;
+}
+
+extern "C" int trs_sptc_unpacked_forward_host(const int32_t* s_column, const float* s_value, const int8_t* s_pos,
+                                              const int32_t* s_window, const int32_t* s_offsets, int groups,
+                                              int num_windows, const trs_half* rhs_host, float* out_host, int window,
+                                              int dimN, int mOri, int kOri, int epoches, trs_timing* timing) {
+    if (!rhs_host || !out_host || groups < 0) return TRS_E_ARG;
+    if (dimN <= 0 || mOri <= 0 || kOri <= 0 || epoches <= 0) return TRS_E_ARG;
+    if (window <= 0 || window > 16) return TRS_E_WINDOW;
+    if (groups > 0 && (!s_column || !s_value || !s_pos)) return TRS_E_ARG;
+    if (!s_offsets && !s_window && groups > 0) return TRS_E_ARG;
+    if (trs_device_count() == 0) return TRS_E_NO_DEVICE;
+    const int W = trs::ceil_div(mOri, window);
+    // per-window group offsets: given, or derived from the per-group window ids (sorted)
+    std::vector<int> off;
+    if (s_offsets) {
+        if (num_windows < 0) return TRS_E_ARG;
+        off.assign(s_offsets, s_offsets + num_windows + 1);
+        if (off[0] != 0) return TRS_E_OFFSETS;
+        if (off[num_windows] != groups) return TRS_E_SHAPE;
+        for (int w = 0; w < num_windows; ++w)
+            if (off[w + 1] < off[w]) return TRS_E_OFFSETS;
+    } else {
+        num_windows = W;
+        off.assign(W + 1, 0);
+        for (int g = 0; g < groups; ++g) {
+            const int w = s_window[g];
+            if (w < 0 || w >= W) return TRS_E_ROW;
+            if (g > 0 && s_window[g - 1] > w) return TRS_E_OFFSETS;
+            off[w + 1]++;
+        }
+        for (int w = 0; w < W; ++w) off[w + 1] += off[w];
+    }
+    std::vector<int> tile_window, tile_group, tile_off(num_windows + 1, 0);
+    for (int w = 0; w < num_windows; ++w) {  // mGCN_online.cpp:914-926
+        for (int g = off[w]; g < off[w + 1]; g += 4) { tile_window.push_back(w); tile_group.push_back(g); }
+        tile_off[w + 1] = (int)tile_window.size();
+    }
+    const int tiles = (int)tile_window.size();
+    Upload up;
+    const int *d_col, *d_off, *d_tw, *d_tg; const float* d_val; const int8_t* d_pos;
+    int rc;
+    if ((rc = up.put(s_column, (size_t)groups * 4, &d_col))) return rc;
+    if ((rc = up.put(s_value, (size_t)groups * window * 2, &d_val))) return rc;
+    if ((rc = up.put(s_pos, (size_t)groups * window * 2, &d_pos))) return rc;
+    if ((rc = up.put(off.data(), off.size(), &d_off))) return rc;
+    if ((rc = up.put(tile_window.data(), tile_window.size(), &d_tw))) return rc;
+    if ((rc = up.put(tile_group.data(), tile_group.size(), &d_tg))) return rc;
+    int* d_tcol; uint32_t *d_pa, *d_pm;
+    if ((rc = up.raw<int>((size_t)tiles * 16, &d_tcol))) return rc;
+    if ((rc = up.raw<uint32_t>((size_t)tiles * 64, &d_pa))) return rc;
+    if ((rc = up.raw<uint32_t>((size_t)tiles * 8, &d_pm))) return rc;
+    if ((rc = trs::pack_tiles(d_col, d_val, d_pos, d_off, d_tw, d_tg, tiles, window, d_tcol, d_pa, d_pm, nullptr))) return rc;
+    TRS_CUDA(cudaDeviceSynchronize());
+    // download the packed tiles and go through the common host path (keeps one code path)
+    std::vector<int> h_tcol((size_t)tiles * 16);
+    std::vector<uint32_t> h_pa((size_t)tiles * 64), h_pm((size_t)tiles * 8);
+    if (tiles) {
+        TRS_CUDA(cudaMemcpy(h_tcol.data(), d_tcol, h_tcol.size() * 4, cudaMemcpyDeviceToHost));
+        TRS_CUDA(cudaMemcpy(h_pa.data(), d_pa, h_pa.size() * 4, cudaMemcpyDeviceToHost));
+        TRS_CUDA(cudaMemcpy(h_pm.data(), d_pm, h_pm.size() * 4, cudaMemcpyDeviceToHost));
+    }
+    trs_format f;
+    memset(&f, 0, sizeof(f));
+    f.s_window_tile_offset = tile_off.data();
+    f.s_tile_column = h_tcol.data();
+    f.s_packed_a = h_pa.data();
+    f.s_packed_meta = h_pm.data();
+    f.num_windows = num_windows;
+    f.tiles = tiles;
+    return trs_spmm_forward_host(&f, rhs_host, out_host, dimN, mOri, kOri, window, epoches, timing);
+}

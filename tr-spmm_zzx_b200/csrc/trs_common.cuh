@@ -1,0 +1,95 @@
+// Shared helpers for libtrspmm's translation units (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "trspmm.h"
+
+#define TRS_CUDA(expr)                                     \
+    do {                                                   \
+        cudaError_t _e = (expr);                           \
+        if (_e != cudaSuccess) return (int)_e;             \
+    } while (0)
+
+#define TRS_LAUNCH_CHECK()                                 \
+    do {                                                   \
+        cudaError_t _e = cudaGetLastError();               \
+        if (_e != cudaSuccess) return (int)_e;             \
+    } while (0)
+
+namespace trs {
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline long long ceil_div64(long long a, long long b) { return (a + b - 1) / b; }
+
+// Simple owning device buffer for plan-lifetime index arrays.
+template <class T>
+struct DevBuf {
+    T* p = nullptr;
+    size_t n = 0;
+    int alloc(size_t count) {
+        n = count;
+        if (count == 0) { p = nullptr; return 0; }
+        cudaError_t e = cudaMalloc((void**)&p, count * sizeof(T));
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        n = 0;
+    }
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// 16-byte asynchronous global->shared copy; src_bytes = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+// D(16x8,f32) += A(16x16 with 2:4 sparsity, stored 16x8 f16) * B(16x8 f16).
+// `meta`: bits 4c..4c+3 = the two kept positions (p0 | p1<<2, p0<p1) of 4-column chunk c for
+// row lane/4; bits 16+4c.. the same for row lane/4+8.  All four lanes of a quad pass the same
+// word, so the thread selector is immaterial.
+__device__ __forceinline__ void mma_sp_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, uint32_t b1,
+                                             uint32_t meta) {
+    asm volatile(
+        "mma.sp::ordered_metadata.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5}, {%6,%7}, {%0,%1,%2,%3}, %8, 0x0;\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(b1), "r"(meta));
+}
+
+// D(16x8,f32) += A(16x16 f16) * B(16x8 f16)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// trs_pack.cu
+int pack_tiles(const int* s_column, const float* s_value, const int8_t* s_pos, const int* s_offset,
+               const int* tile_window, const int* tile_group, long long tiles, int window, int* s_tile_column,
+               uint32_t* packed_a, uint32_t* packed_meta, cudaStream_t st);
+
+}  // namespace trs

@@ -1,0 +1,585 @@
+// Fused per-window SpMM over the reference's hybrid format, for sm_100a.
+//
+// One CTA owns one work item = a 16-row window (or a slice of a heavy window's k-steps) and all
+// F output features of it.  A "k-step" is 16 columns of the window:
+//   * a packed 2:4 tile  (s_tile_column / s_packed_a / s_packed_meta, block_online.cpp:796-841)
+//     -> one mma.sp m16n8k16 per 8 features, or
+//   * a pair of dense 16x8 TC blocks (t_column / t_binary / t_value, block_online.cpp:444-540)
+//     -> one dense mma m16n8k16 per 8 features.
+// The 16 B rows of a step are gathered with 16-byte cp.async into a padded shared-memory tile
+// through a multi-stage pipeline and fed to the tensor cores with ldmatrix.trans; accumulation
+// is fp32 in registers across the whole item.  The CSR remainder parts of the window
+// (c_* / cs_* arrays, block_online.cpp:397-439) are added by the lanes that own the row, and C
+// is written exactly once: no memset, no atomics, no second output buffer, no add kernel
+// (compare mGCNkernel_online.cu:1589-1590, 1689-1712).  Heavy windows are cut into several
+// items that write fp32 partial sums to scratch; a second kernel adds them in a fixed order,
+// so results are bit-identical from run to run.
+#include <cub/device/device_scan.cuh>
+
+#include "trs_common.cuh"
+
+namespace trs {
+
+constexpr int kStages = 4;
+constexpr int kARegionBytes = 768;   // sparse: 256 B A + 32 B meta; dense: 16 rows x 48 B
+constexpr int kDenseRowHalfs = 24;   // 48-byte row stride of the expanded dense A tile
+
+struct Item {
+    int window;      // window id
+    int step_begin;  // k-steps of the window this item covers
+    int step_end;
+    int slot;        // -1: write C; >=0: write partial sums to scratch slot
+};
+
+struct Heavy {
+    int window;
+    int slot_begin;
+    int slot_end;
+};
+
+struct WindowRanges {
+    int* blk_begin;  // TC block range per window
+    int* blk_end;
+    int* c_begin;    // long CSR parts per window
+    int* c_end;
+    int* cs_begin;   // short CSR parts per window
+    int* cs_end;
+};
+
+struct KernelArgs {
+    trs_format f;
+    WindowRanges wr;
+    const Item* items;
+    const __half* B;
+    void* C;
+    float* scratch;
+    int m_rows, k_cols, window, F, out_half;
+};
+
+// ----------------------------------------------------------------------------------------------
+// plan preparation kernels
+// ----------------------------------------------------------------------------------------------
+__global__ void k_part_ranges(const int* __restrict__ key, const int* __restrict__ prefix, int n, int div,
+                              int num_windows, int* __restrict__ begin, int* __restrict__ end, int use_prefix) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n) return;
+    int w = key[p] / div;
+    if (w < 0 || w >= num_windows) return;  // reported by validation
+    int lo = use_prefix ? prefix[p] : p;
+    int hi = use_prefix ? prefix[p + 1] : p + 1;
+    if (p == 0 || key[p - 1] / div != w) begin[w] = lo;
+    if (p == n - 1 || key[p + 1] / div != w) end[w] = hi;
+}
+
+__global__ void k_count_items(trs_format f, WindowRanges wr, int num_windows, int chunk, int* __restrict__ n_items,
+                              int* __restrict__ n_heavy, int* __restrict__ n_slots) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= num_windows) return;
+    int tiles = 0;
+    if (w < f.num_windows) tiles = f.s_window_tile_offset[w + 1] - f.s_window_tile_offset[w];
+    int blocks = wr.blk_end[w] - wr.blk_begin[w];
+    int steps = tiles + (blocks + 1) / 2;
+    int items = steps <= chunk ? 1 : (steps + chunk - 1) / chunk;
+    n_items[w] = items;
+    n_heavy[w] = items > 1 ? 1 : 0;
+    n_slots[w] = items > 1 ? items : 0;
+}
+
+__global__ void k_fill_items(trs_format f, WindowRanges wr, int num_windows, int chunk,
+                             const int* __restrict__ item_off, const int* __restrict__ heavy_off,
+                             const int* __restrict__ slot_off, Item* __restrict__ items, Heavy* __restrict__ heavy) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= num_windows) return;
+    int tiles = 0;
+    if (w < f.num_windows) tiles = f.s_window_tile_offset[w + 1] - f.s_window_tile_offset[w];
+    int blocks = wr.blk_end[w] - wr.blk_begin[w];
+    int steps = tiles + (blocks + 1) / 2;
+    int n = item_off[w + 1] - item_off[w];
+    if (n == 1) {
+        items[item_off[w]] = Item{w, 0, steps, -1};
+        return;
+    }
+    // split evenly so that no item is much shorter than the others
+    int per = (steps + n - 1) / n;
+    for (int i = 0; i < n; ++i) {
+        int b = min(i * per, steps), e = min(b + per, steps);
+        items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i};
+    }
+    heavy[heavy_off[w]] = Heavy{w, slot_off[w], slot_off[w] + n};
+}
+
+// Validation: every violated rule ORs one bit into *err.
+enum { V_OFFSETS = 1, V_COLUMN = 2, V_ROW = 4, V_SHAPE = 8 };
+
+__global__ void k_check_prefix(const int* __restrict__ a, int n, int expect_last, int* err) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (i == 0 && a[0] != 0) atomicOr(err, V_OFFSETS);
+    if (i + 1 < n && a[i + 1] < a[i]) atomicOr(err, V_OFFSETS);
+    if (i == n - 1 && expect_last >= 0 && a[i] != expect_last) atomicOr(err, V_SHAPE);
+}
+__global__ void k_check_range(const int* __restrict__ a, long long n, int lo, int hi, int bit, int* err) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int v = a[i];
+    if (v < lo || v >= hi) atomicOr(err, bit);
+}
+__global__ void k_check_sorted(const int* __restrict__ a, int n, int* err) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i + 1 < n && a[i + 1] < a[i]) atomicOr(err, V_OFFSETS);
+}
+
+// ----------------------------------------------------------------------------------------------
+// the fused window kernel
+// ----------------------------------------------------------------------------------------------
+template <int WARPS>
+struct Tile {
+    static constexpr int FS = WARPS * 32;          // features per CTA
+    static constexpr int ROWB = FS * 2 + 16;       // padded B-row bytes: conflict-free ldmatrix
+    static constexpr int BBYTES = 16 * ROWB;
+    static constexpr int STAGE = BBYTES + kARegionBytes;
+    static constexpr int SMEM = STAGE * kStages;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int CPR = FS / 8;             // 16-byte chunks per B row
+};
+
+template <int WARPS, bool ALIGNED>
+__global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) {
+    using T = Tile<WARPS>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int g = lane >> 2;   // fragment row group
+    const int t = lane & 3;    // thread in group
+    const int fbase = blockIdx.y * T::FS;
+
+    const Item it = a.items[blockIdx.x];
+    const int w = it.window;
+    const int tile0 = (w < a.f.num_windows) ? a.f.s_window_tile_offset[w] : 0;
+    const int ntiles = (w < a.f.num_windows) ? a.f.s_window_tile_offset[w + 1] - tile0 : 0;
+    const int blk0 = a.wr.blk_begin[w];
+    const int blk_end = a.wr.blk_end[w];
+    const int nsteps = it.step_end - it.step_begin;
+    const size_t F = (size_t)a.F;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    // column id of B-row `k` (0..15) of window step `s`
+    auto step_col = [&](int s, int k) -> int {
+        if (s < ntiles) return __ldg(a.f.s_tile_column + (size_t)(tile0 + s) * 16 + k);
+        int b = blk0 + 2 * (s - ntiles) + (k >> 3);
+        return b < blk_end ? __ldg(a.f.t_column + (size_t)b * 8 + (k & 7)) : -1;
+    };
+
+    // each thread copies chunk (row0, ch) and (row0 + 8, ch) of every step when ALIGNED
+    const int ch = tid % T::CPR;
+    const int row0 = tid / T::CPR;  // 0..7
+    int pre0 = -1, pre1 = -1;       // prefetched column ids for the next step to issue
+    if (ALIGNED && nsteps > 0) {
+        pre0 = step_col(it.step_begin, row0);
+        pre1 = step_col(it.step_begin, row0 + 8);
+    }
+
+    auto issue = [&](int j) {  // j: step index relative to the item
+        const int s = it.step_begin + j;
+        unsigned char* st = smem + (j % kStages) * T::STAGE;
+        // ---- B rows
+        if (ALIGNED) {
+            const int c0 = pre0, c1 = pre1;
+            if (j + 1 < nsteps) {  // prefetch the next step's column ids before they are needed
+                pre0 = step_col(s + 1, row0);
+                pre1 = step_col(s + 1, row0 + 8);
+            }
+            const int f = fbase + ch * 8;
+            const bool fin = f < a.F;  // F % 8 == 0 here, so a chunk is inside or outside
+            const __half* src0 = (c0 >= 0 && fin) ? a.B + (size_t)c0 * F + f : a.B;
+            const __half* src1 = (c1 >= 0 && fin) ? a.B + (size_t)c1 * F + f : a.B;
+            cp_async16(smem_u32(st + row0 * T::ROWB + ch * 16), src0, (c0 >= 0 && fin) ? 16 : 0);
+            cp_async16(smem_u32(st + (row0 + 8) * T::ROWB + ch * 16), src1, (c1 >= 0 && fin) ? 16 : 0);
+        } else {
+            for (int i = tid; i < 16 * T::FS; i += T::THREADS) {
+                const int r = i / T::FS, fo = i % T::FS;
+                const int c = step_col(s, r);
+                __half v = __float2half(0.f);
+                if (c >= 0 && fbase + fo < a.F) v = a.B[(size_t)c * F + fbase + fo];
+                *(__half*)(st + r * T::ROWB + fo * 2) = v;
+            }
+        }
+        // ---- A operand
+        unsigned char* as = st + T::BBYTES;
+        if (s < ntiles) {
+            const size_t tile = (size_t)(tile0 + s);
+            if (tid < 16) cp_async16(smem_u32(as + tid * 16), a.f.s_packed_a + tile * 64 + tid * 4, 16);
+            else if (tid < 18) cp_async16(smem_u32(as + 256 + (tid - 16) * 16), a.f.s_packed_meta + tile * 8 + (tid - 16) * 4, 16);
+        } else {
+            const int b0 = blk0 + 2 * (s - ntiles);
+            for (int i = tid; i < 256; i += T::THREADS) {
+                const int r = i >> 4, k = i & 15;
+                const int b = b0 + (k >> 3);
+                __half v = __float2half(0.f);
+                if (b < blk_end) {
+                    const unsigned long long lo = (unsigned long long)a.f.t_binary[(size_t)b * 2];
+                    const unsigned long long hi = (unsigned long long)a.f.t_binary[(size_t)b * 2 + 1];
+                    const int bit = (r & 7) * 8 + (k & 7);
+                    const unsigned long long m = r < 8 ? lo : hi;
+                    if ((m >> bit) & 1ull) {
+                        int rank = __popcll(m & ((1ull << bit) - 1ull));
+                        if (r >= 8) rank += __popcll(lo);
+                        v = ((const __half*)a.f.t_value)[(size_t)a.f.t_block_offset[b] + rank];
+                    }
+                }
+                ((__half*)as)[r * kDenseRowHalfs + k] = v;
+            }
+        }
+    };
+
+    auto compute = [&](int j) {
+        const int s = it.step_begin + j;
+        const unsigned char* st = smem + (j % kStages) * T::STAGE;
+        const unsigned char* as = st + T::BBYTES;
+        // ldmatrix row address of this lane: matrix m = lane/8 -> k rows (m&1)*8.., features (m>>1)*8..
+        const int m = lane >> 3;
+        const int krow = (lane & 7) + (m & 1) * 8;
+        const uint32_t baddr = smem_u32(st + krow * T::ROWB + (wid * 32 + (m >> 1) * 8) * 2);
+        if (s < ntiles) {
+            const uint2 av = *(const uint2*)(as + lane * 8);
+            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+            }
+        } else {
+            const uint32_t a0 = *(const uint32_t*)(as + g * 48 + t * 4);
+            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 48 + t * 4);
+            const uint32_t a2 = *(const uint32_t*)(as + g * 48 + 16 + t * 4);
+            const uint32_t a3 = *(const uint32_t*)(as + (g + 8) * 48 + 16 + t * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+    };
+
+    // ---- software pipeline over the k-steps ------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < kStages - 1; ++j) {
+        if (j < nsteps) issue(j);
+        cp_async_commit();
+    }
+    for (int j = 0; j < nsteps; ++j) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        if (j + kStages - 1 < nsteps) issue(j + kStages - 1);
+        cp_async_commit();
+        compute(j);
+    }
+    cp_async_wait<0>();
+
+    // ---- CSR remainder parts: added by the first item of the window --------------------------
+    if (it.step_begin == 0) {
+        const int fcol = fbase + wid * 32 + 2 * t;  // + 8*n
+        for (int pass = 0; pass < 2; ++pass) {
+            const int pb = pass ? a.wr.cs_begin[w] : a.wr.c_begin[w];
+            const int pe = pass ? a.wr.cs_end[w] : a.wr.c_end[w];
+            const int* roff = pass ? a.f.cs_row_offset : a.f.c_row_offset;
+            const int* rrow = pass ? a.f.cs_row : a.f.c_row;
+            const int* rcol = pass ? a.f.cs_column : a.f.c_column;
+            const __half* rval = (const __half*)(pass ? a.f.cs_value : a.f.c_value);
+            for (int p = pb; p < pe; ++p) {
+                const int lr = rrow[p] - w * a.window;
+                if ((lr & 7) != g || lr < 0 || lr >= 16) continue;
+                const int hi = lr >> 3;
+                for (int e = roff[p]; e < roff[p + 1]; ++e) {
+                    const int c = rcol[e];
+                    const float v = __half2float(rval[e]);
+                    const __half* brow = a.B + (size_t)c * F;
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) {
+                        const int f = fcol + n * 8;
+                        const float x0 = f < a.F ? v * __half2float(brow[f]) : 0.f;
+                        const float x1 = f + 1 < a.F ? v * __half2float(brow[f + 1]) : 0.f;
+                        if (hi) { acc[n][2] += x0; acc[n][3] += x1; }
+                        else { acc[n][0] += x0; acc[n][1] += x1; }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- epilogue ----------------------------------------------------------------------------
+    const int fcol = fbase + wid * 32 + 2 * t;
+    if (it.slot >= 0) {
+        float* dst = a.scratch + (size_t)it.slot * 16 * F;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int f = fcol + n * 8;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float* d = dst + (size_t)(g + 8 * h) * F + f;
+                if (f < a.F) d[0] = acc[n][2 * h];
+                if (f + 1 < a.F) d[1] = acc[n][2 * h + 1];
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int lr = g + 8 * h;
+        const long long row = (long long)w * a.window + lr;
+        if (lr >= a.window || row >= a.m_rows) continue;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            const int f = fcol + n * 8;
+            if (a.out_half) {
+                __half* d = (__half*)a.C + (size_t)row * F + f;
+                if (f + 1 < a.F && (a.F & 1) == 0) *(__half2*)d = __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]);
+                else {
+                    if (f < a.F) d[0] = __float2half_rn(acc[n][2 * h]);
+                    if (f + 1 < a.F) d[1] = __float2half_rn(acc[n][2 * h + 1]);
+                }
+            } else {
+                float* d = (float*)a.C + (size_t)row * F + f;
+                if (f + 1 < a.F && (a.F & 1) == 0) *(float2*)d = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+                else {
+                    if (f < a.F) d[0] = acc[n][2 * h];
+                    if (f + 1 < a.F) d[1] = acc[n][2 * h + 1];
+                }
+            }
+        }
+    }
+}
+
+// Adds the partial sums of a split window in slot order and writes its 16 rows of C.
+__global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __restrict__ scratch, void* C, int F,
+                               int m_rows, int window, int out_half) {
+    const Heavy h = heavy[blockIdx.x];
+    const int per = 16 * F;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int lr = i / F, f = i % F;
+        const long long row = (long long)h.window * window + lr;
+        if (lr >= window || row >= m_rows) continue;
+        float s = 0.f;
+        for (int sl = h.slot_begin; sl < h.slot_end; ++sl) s += scratch[(size_t)sl * per + i];
+        if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
+        else ((float*)C)[(size_t)row * F + f] = s;
+    }
+}
+
+}  // namespace trs
+
+// ----------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------
+using namespace trs;
+
+struct trs_spmm_plan {
+    trs_format f;
+    int m_rows, k_cols, window, num_windows, chunk;
+    DevBuf<int> ranges;  // 6 * num_windows
+    WindowRanges wr;
+    DevBuf<Item> items;
+    DevBuf<Heavy> heavy;
+    int n_items, n_heavy, n_slots;
+};
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+static int validate_on_device(const trs_format& f, int m_rows, int k_cols, int window, int num_windows,
+                              cudaStream_t st) {
+    int* d_err = nullptr;
+    TRS_CUDA(cudaMalloc(&d_err, sizeof(int)));
+    cudaMemsetAsync(d_err, 0, sizeof(int), st);
+    auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
+    if (f.parts_t > 0) {
+        k_check_prefix<<<grid(f.parts_t + 1), 256, 0, st>>>(f.t_row_offset, f.parts_t + 1, f.blocks, d_err);
+        k_check_prefix<<<grid(f.blocks + 1), 256, 0, st>>>(f.t_block_offset, f.blocks + 1, -1, d_err);
+        k_check_range<<<grid((long long)f.blocks * 8), 256, 0, st>>>(f.t_column, (long long)f.blocks * 8, -1, k_cols, V_COLUMN, d_err);
+        k_check_range<<<grid(f.parts_t), 256, 0, st>>>(f.t_window_row, f.parts_t, 0, num_windows * 16, V_ROW, d_err);
+        k_check_sorted<<<grid(f.parts_t), 256, 0, st>>>(f.t_window_row, f.parts_t, d_err);
+    }
+    for (int pass = 0; pass < 2; ++pass) {
+        const int n = pass ? f.parts_c_short : f.parts_c;
+        if (n <= 0) continue;
+        const int* off = pass ? f.cs_row_offset : f.c_row_offset;
+        const int* row = pass ? f.cs_row : f.c_row;
+        k_check_prefix<<<grid(n + 1), 256, 0, st>>>(off, n + 1, -1, d_err);
+        k_check_range<<<grid(n), 256, 0, st>>>(row, n, 0, m_rows, V_ROW, d_err);
+        k_check_sorted<<<grid(n), 256, 0, st>>>(row, n, d_err);
+    }
+    // column ids of the CSR parts: their count is the last prefix entry, which lives on the device
+    for (int pass = 0; pass < 2; ++pass) {
+        const int n = pass ? f.parts_c_short : f.parts_c;
+        if (n <= 0) continue;
+        int last = 0;
+        cudaError_t e2 = cudaMemcpyAsync(&last, (pass ? f.cs_row_offset : f.c_row_offset) + n, sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (e2 == cudaSuccess) e2 = cudaStreamSynchronize(st);
+        if (e2 != cudaSuccess) { cudaFree(d_err); return (int)e2; }
+        if (last > 0)
+            k_check_range<<<grid(last), 256, 0, st>>>(pass ? f.cs_column : f.c_column, last, 0, k_cols, V_COLUMN, d_err);
+    }
+    if (f.num_windows > 0) {
+        k_check_prefix<<<grid(f.num_windows + 1), 256, 0, st>>>(f.s_window_tile_offset, f.num_windows + 1, f.tiles, d_err);
+        if (f.tiles > 0)
+            k_check_range<<<grid((long long)f.tiles * 16), 256, 0, st>>>(f.s_tile_column, (long long)f.tiles * 16, -1, k_cols, V_COLUMN, d_err);
+    }
+    int h_err = 0;
+    cudaError_t e = cudaMemcpyAsync(&h_err, d_err, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_err);
+    if (e != cudaSuccess) return (int)e;
+    if (h_err & V_OFFSETS) return TRS_E_OFFSETS;
+    if (h_err & V_SHAPE) return TRS_E_SHAPE;
+    if (h_err & V_COLUMN) return TRS_E_COLUMN;
+    if (h_err & V_ROW) return TRS_E_ROW;
+    return TRS_OK;
+}
+
+// CSR value-count checks need the last prefix entry; done with the column range check so that a
+// short column array cannot be over-read: the caller states the lengths implicitly through the
+// prefix arrays, exactly as the reference does (mGCN_online.cpp:982-1042 copies numel() items).
+extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, int k_cols, int window, int validate,
+                                    void* stream, trs_spmm_plan** out_plan) {
+    if (!dev_format || !out_plan) return TRS_E_ARG;
+    *out_plan = nullptr;
+    if (m_rows <= 0 || k_cols <= 0) return TRS_E_ARG;
+    if (window <= 0 || window > 16) return TRS_E_WINDOW;
+    const trs_format& f = *dev_format;
+    if (f.parts_t < 0 || f.blocks < 0 || f.parts_c < 0 || f.parts_c_short < 0 || f.num_windows < 0 || f.tiles < 0)
+        return TRS_E_ARG;
+    if (f.blocks > 0 && window != 16) return TRS_E_WINDOW;  // TC parts address rows as window_id * 16
+    if (f.parts_t > 0 && !(f.t_row_offset && f.t_block_offset && f.t_column && f.t_value && f.t_window_row && f.t_binary))
+        return TRS_E_ARG;
+    if (f.parts_c > 0 && !(f.c_row_offset && f.c_row && f.c_column && f.c_value)) return TRS_E_ARG;
+    if (f.parts_c_short > 0 && !(f.cs_row_offset && f.cs_row && f.cs_column && f.cs_value)) return TRS_E_ARG;
+    if (f.num_windows > 0 && !f.s_window_tile_offset) return TRS_E_ARG;
+    if (f.tiles > 0 && !(f.s_tile_column && f.s_packed_a && f.s_packed_meta)) return TRS_E_ARG;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return TRS_E_NO_DEVICE;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    const int W = max(ceil_div(m_rows, window), f.num_windows);
+    if (validate) {
+        int rc = validate_on_device(f, m_rows, k_cols, window, W, st);
+        if (rc != TRS_OK) return rc;
+    }
+
+    trs_spmm_plan* p = new trs_spmm_plan();
+    p->f = f;
+    p->m_rows = m_rows; p->k_cols = k_cols; p->window = window; p->num_windows = W;
+    p->chunk = max(8, env_int("TRS_CHUNK_STEPS", 256));
+    int rc = p->ranges.alloc((size_t)6 * W);
+    if (rc) { delete p; return rc; }
+    cudaMemsetAsync(p->ranges.p, 0, sizeof(int) * 6 * W, st);
+    p->wr = WindowRanges{p->ranges.p, p->ranges.p + W, p->ranges.p + 2 * W, p->ranges.p + 3 * W,
+                         p->ranges.p + 4 * W, p->ranges.p + 5 * W};
+    auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
+    if (f.parts_t > 0)
+        k_part_ranges<<<grid(f.parts_t), 256, 0, st>>>(f.t_window_row, f.t_row_offset, f.parts_t, 16, W,
+                                                        p->wr.blk_begin, p->wr.blk_end, 1);
+    if (f.parts_c > 0)
+        k_part_ranges<<<grid(f.parts_c), 256, 0, st>>>(f.c_row, nullptr, f.parts_c, window, W, p->wr.c_begin, p->wr.c_end, 0);
+    if (f.parts_c_short > 0)
+        k_part_ranges<<<grid(f.parts_c_short), 256, 0, st>>>(f.cs_row, nullptr, f.parts_c_short, window, W,
+                                                              p->wr.cs_begin, p->wr.cs_end, 0);
+    // counts -> exclusive scans (three arrays of W + 1)
+    DevBuf<int> cnt, off;
+    DevBuf<unsigned char> tmp;
+    rc = cnt.alloc((size_t)3 * (W + 1));
+    if (!rc) rc = off.alloc((size_t)3 * (W + 1));
+    size_t tmp_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt.p, off.p, W + 1, st);
+    if (!rc) rc = tmp.alloc(tmp_bytes + 16);
+    auto fail = [&](int code) { cnt.release(); off.release(); tmp.release(); trs_spmm_plan_destroy(p); return code; };
+    if (rc) return fail(rc);
+    cudaMemsetAsync(cnt.p, 0, sizeof(int) * 3 * (W + 1), st);
+    k_count_items<<<grid(W), 256, 0, st>>>(f, p->wr, W, p->chunk, cnt.p, cnt.p + (W + 1), cnt.p + 2 * (W + 1));
+    for (int i = 0; i < 3; ++i)
+        cub::DeviceScan::ExclusiveSum(tmp.p, tmp_bytes, cnt.p + (size_t)i * (W + 1), off.p + (size_t)i * (W + 1), W + 1, st);
+    int totals[3] = {0, 0, 0};
+    for (int i = 0; i < 3; ++i)
+        cudaMemcpyAsync(&totals[i], off.p + (size_t)i * (W + 1) + W, sizeof(int), cudaMemcpyDeviceToHost, st);
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail((int)e);
+    p->n_items = totals[0]; p->n_heavy = totals[1]; p->n_slots = totals[2];
+    rc = p->items.alloc(p->n_items);
+    if (!rc) rc = p->heavy.alloc(p->n_heavy);
+    if (rc) return fail(rc);
+    k_fill_items<<<grid(W), 256, 0, st>>>(f, p->wr, W, p->chunk, off.p, off.p + (W + 1), off.p + 2 * (W + 1),
+                                           p->items.p, p->heavy.p);
+    e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    cnt.release(); off.release(); tmp.release();
+    if (e != cudaSuccess) { trs_spmm_plan_destroy(p); return (int)e; }
+    *out_plan = p;
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
+    if (!p) return TRS_OK;
+    p->ranges.release();
+    p->items.release();
+    p->heavy.release();
+    delete p;
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_workspace_bytes(const trs_spmm_plan* p, int F, size_t* bytes) {
+    if (!p || !bytes || F <= 0) return TRS_E_ARG;
+    *bytes = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_launches(const trs_spmm_plan* p) { return p ? (p->n_heavy > 0 ? 2 : 1) : 0; }
+
+template <int WARPS>
+static int launch_window_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
+    using T = Tile<WARPS>;
+    const bool aligned = (a.F % 8 == 0) && (((uintptr_t)a.B & 15) == 0);
+    dim3 grid(n_items, ceil_div(a.F, T::FS));
+    if (aligned) {
+        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+        k_window_spmm<WARPS, true><<<grid, T::THREADS, T::SMEM, st>>>(a);
+    } else {
+        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+        k_window_spmm<WARPS, false><<<grid, T::THREADS, T::SMEM, st>>>(a);
+    }
+    TRS_LAUNCH_CHECK();
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+    if (!p || !B || !C || F <= 0) return TRS_E_ARG;
+    if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
+    size_t need = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    KernelArgs a;
+    a.f = p->f; a.wr = p->wr; a.items = p->items.p;
+    a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
+    a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
+    int rc;
+    if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, st);
+    else if (F <= 64) rc = launch_window_kernel<2>(a, p->n_items, st);
+    else rc = launch_window_kernel<4>(a, p->n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
+    if (rc) return rc;
+    if (p->n_heavy > 0) {
+        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half);
+        TRS_LAUNCH_CHECK();
+    }
+    return TRS_OK;
+}

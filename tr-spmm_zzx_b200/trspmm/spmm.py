@@ -1,0 +1,133 @@
+"""SpMM over the hybrid format: plan/run on device tensors, and the host-buffer entries."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .format import Format
+
+OUT_F32, OUT_F16 = 0, 1
+
+
+def _out_code(dtype) -> int:
+    if dtype == torch.float32:
+        return OUT_F32
+    if dtype == torch.float16:
+        return OUT_F16
+    raise TypeError("output dtype must be torch.float32 or torch.float16")
+
+
+class SpmmPlan:
+    """Device-resident plan (trs_spmm_plan_create): replaces the device half of
+    Libra6SpMMOnline.forward_fp16_tcu_cuda_sptc_mma_parallel_online
+    (TR-source/SpMM/mGCN_online.cpp:760-1138).  The format tensors must be CUDA tensors and
+    stay alive as long as the plan."""
+
+    def __init__(self, fmt: Format, m_rows: int, k_cols: int, window: int = 16, validate: bool = True):
+        if fmt.device.type != "cuda":
+            raise ValueError("SpmmPlan needs the format on a CUDA device (use spmm_forward_host for CPU tensors)")
+        self.lib = _lib.load()
+        self.fmt = fmt.half_values().contiguous()
+        self.m_rows, self.k_cols, self.window = int(m_rows), int(k_cols), int(window)
+        self.device = self.fmt.device
+        self._handle = C.c_void_p()
+        self._ws = {}
+        with torch.cuda.device(self.device):
+            cf = self.fmt.c_struct()
+            _lib.check(self.lib.trs_spmm_plan_create(C.byref(cf), self.m_rows, self.k_cols, self.window,
+                                                     int(validate), _lib.current_stream_ptr(self.device),
+                                                     C.byref(self._handle)))
+
+    def workspace_bytes(self, F: int) -> int:
+        n = C.c_size_t()
+        _lib.check(self.lib.trs_spmm_workspace_bytes(self._handle, int(F), C.byref(n)))
+        return n.value
+
+    @property
+    def launches(self) -> int:
+        return self.lib.trs_spmm_launches(self._handle)
+
+    def run(self, B: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float16) -> torch.Tensor:
+        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
+            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
+        if B.shape[0] != self.k_cols:
+            raise ValueError(f"B has {B.shape[0]} rows, the plan expects {self.k_cols}")
+        F = B.shape[1]
+        if out is None:
+            out = torch.empty((self.m_rows, F), dtype=out_dtype, device=self.device)
+        elif out.shape != (self.m_rows, F) or not out.is_contiguous() or out.device != self.device:
+            raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
+        ws = self._ws.get(F)
+        if ws is None:
+            ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
+            self._ws[F] = ws
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.trs_spmm_run(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
+                                             ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(self.device)))
+        return out
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle:
+            self.lib.trs_spmm_plan_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _cpu_format(fmt: Format) -> Format:
+    if fmt.device.type != "cpu":
+        raise ValueError("the host-buffer entry takes CPU tensors")
+    return fmt.half_values().contiguous()
+
+
+def spmm_forward_host(fmt: Format, rhs: torch.Tensor, dimN: int, mOri: int, kOri: int, window: int = 16,
+                      epoches: int = 1):
+    """trs_spmm_forward_host: CPU tensors in, fp32 CPU result out; everything is uploaded, run
+    `epoches` times and released inside the call, like the reference entry it mirrors."""
+    lib = _lib.load()
+    f = _cpu_format(fmt)
+    rhs = rhs.contiguous()
+    out = torch.empty((mOri, dimN), dtype=torch.float32)
+    timing = _lib.TrsTiming()
+    cf = f.c_struct()
+    _lib.check(lib.trs_spmm_forward_host(C.byref(cf), rhs.data_ptr(), out.data_ptr(), dimN, mOri, kOri, window,
+                                         epoches, C.byref(timing)))
+    return out, timing
+
+
+class ResidentSpmm:
+    """trs_resident_*: the format is uploaded once; each forward copies B host->device, runs,
+    and copies C device->host.  For host-resident callers that reuse one matrix."""
+
+    def __init__(self, fmt: Format, mOri: int, kOri: int, window: int = 16, max_dimN: int = 256):
+        self.lib = _lib.load()
+        self._keep = _cpu_format(fmt)
+        self._handle = C.c_void_p()
+        self.mOri, self.kOri, self.max_dimN = mOri, kOri, max_dimN
+        cf = self._keep.c_struct()
+        _lib.check(self.lib.trs_resident_create(C.byref(cf), mOri, kOri, window, max_dimN, C.byref(self._handle)))
+
+    def forward(self, rhs: torch.Tensor, out: torch.Tensor):
+        if rhs.device.type != "cpu" or out.device.type != "cpu":
+            raise ValueError("ResidentSpmm.forward takes host tensors")
+        timing = _lib.TrsTiming()
+        _lib.check(self.lib.trs_resident_forward(self._handle, rhs.data_ptr(), out.data_ptr(), rhs.shape[1],
+                                                 _out_code(out.dtype), C.byref(timing)))
+        return out, timing
+
+    def close(self):
+        if self._handle:
+            self.lib.trs_resident_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
