@@ -102,6 +102,9 @@ int trs_spmm_workspace_bytes(const trs_spmm_plan* plan, int F, size_t* bytes);
  * needed), fp32 or fp16 per out_dtype.  Asynchronous on `stream`; allocates nothing. */
 int trs_spmm_run(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* Health word of the plan's kernels: 0, or non-zero when a bounded pipeline wait inside a kernel
+ * gave up (the affected call's output is then incomplete).  Synchronises the device. */
+int trs_spmm_status(const trs_spmm_plan* plan, int* status);
 /* Number of kernels one trs_spmm_run launches (1, or 2 when some window is split). */
 int trs_spmm_launches(const trs_spmm_plan* plan);
 
@@ -132,6 +135,50 @@ int trs_sptc_unpacked_forward_host(const int32_t* s_column, const float* s_value
                                    int num_windows, const trs_half* rhs_host, float* out_host,
                                    int window, int dimN, int mOri, int kOri, int epoches,
                                    trs_timing* timing);
+
+/* ---- format builder ---------------------------------------------------------------------------
+ * Replaces Libra5BlockOnline.block_sptc_2to4_online (block_online.cpp:545-871): device CSR in,
+ * the 29 arrays of block_online.cpp:844-870 out, bit-exact, built by GPU kernels.  `wide`,
+ * `sptc_min_util` and `sptc_threshold` of the reference signature are accepted by the Python
+ * shim and ignored here exactly as the reference ignores them (block_online.cpp:548-553).
+ * skip_tc / unit_min_nnz carry the reference's LIBRA_SKIP_TC / LIBRA_SPTC_UNIT_MIN_NNZ
+ * environment switches (block_online.cpp:564-567).  Input must be canonical CSR (columns
+ * strictly ascending inside each row), which is what the reference's caller produces. */
+#define TRS_BUILD_NUM_ARRAYS 29
+typedef struct trs_build_config {
+    int32_t part_t;      /* partSize_t: TC blocks per part                 */
+    int32_t part_c;      /* partSize_c: entries per long CUDA-core part    */
+    int32_t short_size;  /* shortSize: longest short CUDA-core part        */
+    int32_t density;     /* minimum rows per column for a TC column        */
+    int32_t window;      /* rows per window, 1..16                         */
+    float tc_min_util;   /* minimum nnz / (window * 8) of a kept TC chunk  */
+    int32_t skip_tc;     /* LIBRA_SKIP_TC                                  */
+    int32_t unit_min_nnz;/* LIBRA_SPTC_UNIT_MIN_NNZ (reference default 2)  */
+} trs_build_config;
+
+typedef struct trs_build_stats_t {
+    long long nnz, dropped_nnz, distinct_window_columns, units;
+    long long tc_nnz, csr_nnz, groups, tiles, tc_blocks;
+    float build_ms; /* device time of the whole build */
+} trs_build_stats_t;
+
+typedef struct trs_builder trs_builder; /* opaque; owns the output arrays on the device */
+
+int trs_build_create(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
+                     const trs_build_config* cfg, void* stream, trs_builder** out);
+int trs_build_destroy(trs_builder* b);
+/* element counts of the 29 arrays, in the reference's return order */
+int trs_build_sizes(const trs_builder* b, long long sizes[TRS_BUILD_NUM_ARRAYS]);
+int trs_build_stats(const trs_builder* b, trs_build_stats_t* stats);
+/* device pointer of array `id` (owned by the builder) */
+const void* trs_build_array(const trs_builder* b, int id);
+/* copy array `id` into caller memory (host or device) */
+int trs_build_copy(const trs_builder* b, int id, void* dst, int dst_is_host, void* stream);
+/* trs_format over the builder's arrays with the value arrays converted to fp16 (what
+ * mdataset2_online.py:151-153 does on the host); valid until the builder is destroyed */
+int trs_build_format(trs_builder* b, trs_format* out, void* stream);
+/* the std::sort emulation used by the matching stage, run on the host (test hook) */
+int trs_debug_stdsort_order(const unsigned char* keys, int n, int* out, int* heap_sorts);
 
 /* ---- SDDMM (no counterpart in the reference; defined by BASELINE config 3) -----------------
  * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e. */

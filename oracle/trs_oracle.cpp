@@ -507,4 +507,19 @@ void trs_oracle_std_sort_order(const int* keys, int n, int* out) {
 
 uint16_t trs_oracle_f32_to_f16(float f) { return f32_to_f16_bits(f); }
 
+// McIlroy's "killer adversary" played against libstdc++'s std::sort with a descending
+// comparator: the returned keys make that same sort exhaust its depth limit.
+void trs_oracle_adversary(int n, int* keys) {
+    std::vector<int> val(n, n - 1), perm(n);
+    const int gas = n - 1;
+    int nsolid = 0, candidate = 0;
+    for (int i = 0; i < n; ++i) perm[i] = i;
+    std::sort(perm.begin(), perm.end(), [&](int x, int y) {
+        if (val[x] == gas && val[y] == gas) { if (x == candidate) val[x] = nsolid++; else val[y] = nsolid++; }
+        if (val[x] == gas) candidate = x; else if (val[y] == gas) candidate = y;
+        return val[x] < val[y];
+    });
+    for (int i = 0; i < n; ++i) keys[i] = n - val[i];  // descending comparator sees the same order
+}
+
 }  // extern "C"

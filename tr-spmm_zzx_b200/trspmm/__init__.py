@@ -9,3 +9,4 @@ from ._lib import TrsError, lib_path, load  # noqa: F401
 from .format import FORMAT_NAMES, Format  # noqa: F401
 from .spmm import SpmmPlan, spmm_forward_host, ResidentSpmm  # noqa: F401
 from .sddmm import sddmm  # noqa: F401
+from .builder import build_format  # noqa: F401

@@ -35,6 +35,16 @@ class TrsFormat(C.Structure):
     ]
 
 
+class TrsBuildConfig(C.Structure):
+    _fields_ = [("part_t", C.c_int32), ("part_c", C.c_int32), ("short_size", C.c_int32), ("density", C.c_int32),
+                ("window", C.c_int32), ("tc_min_util", C.c_float), ("skip_tc", C.c_int32), ("unit_min_nnz", C.c_int32)]
+
+
+class TrsBuildStats(C.Structure):
+    _fields_ = [(n, C.c_longlong) for n in ("nnz", "dropped_nnz", "distinct_window_columns", "units", "tc_nnz",
+                                            "csr_nnz", "groups", "tiles", "tc_blocks")] + [("build_ms", C.c_float)]
+
+
 class TrsTiming(C.Structure):
     _fields_ = [(n, C.c_float) for n in
                 ("total_ms", "tc_ms", "cuda_long_ms", "cuda_short_ms", "sptc_ms", "h2d_ms", "d2h_ms")]
@@ -71,9 +81,21 @@ def load():
     lib.trs_sptc_unpacked_forward_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32,
                                                    C.POINTER(TrsTiming)]
     lib.trs_sddmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
+    lib.trs_spmm_status.argtypes = [vp, C.POINTER(i32)]
+    lib.trs_build_create.argtypes = [vp, vp, vp, i32, C.POINTER(TrsBuildConfig), vp, C.POINTER(vp)]
+    lib.trs_build_destroy.argtypes = [vp]
+    lib.trs_build_sizes.argtypes = [vp, C.POINTER(C.c_longlong)]
+    lib.trs_build_stats.argtypes = [vp, C.POINTER(TrsBuildStats)]
+    lib.trs_build_array.argtypes = [vp, i32]
+    lib.trs_build_array.restype = vp
+    lib.trs_build_copy.argtypes = [vp, i32, vp, i32, vp]
+    lib.trs_build_format.argtypes = [vp, C.POINTER(TrsFormat), vp]
+    lib.trs_debug_stdsort_order.argtypes = [vp, i32, vp, C.POINTER(i32)]
     for name in ("trs_spmm_plan_create", "trs_spmm_plan_destroy", "trs_spmm_workspace_bytes", "trs_spmm_run",
                  "trs_spmm_launches", "trs_spmm_forward_host", "trs_resident_create", "trs_resident_forward",
-                 "trs_resident_destroy", "trs_sptc_unpacked_forward_host", "trs_sddmm"):
+                 "trs_resident_destroy", "trs_sptc_unpacked_forward_host", "trs_sddmm", "trs_spmm_status",
+                 "trs_build_create", "trs_build_destroy", "trs_build_sizes", "trs_build_stats", "trs_build_copy",
+                 "trs_build_format", "trs_debug_stdsort_order"):
         getattr(lib, name).restype = i32
     _LIB = lib
     return lib

@@ -45,6 +45,12 @@ class SpmmPlan:
         _lib.check(self.lib.trs_spmm_workspace_bytes(self._handle, int(F), C.byref(n)))
         return n.value
 
+    def status(self) -> int:
+        """0, or non-zero when a bounded wait inside a kernel gave up (synchronises the device)."""
+        v = C.c_int()
+        _lib.check(self.lib.trs_spmm_status(self._handle, C.byref(v)))
+        return v.value
+
     @property
     def launches(self) -> int:
         return self.lib.trs_spmm_launches(self._handle)
