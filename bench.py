@@ -1,0 +1,337 @@
+#!/usr/bin/env python3
+"""Benchmark of the hybrid sparse hot path: SpMM GFLOP/s (2*nnz*F) and HBM roofline fraction.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A "step" is one SpMM pass C = A'.B of the whole matrix through the fused window kernel, with the
+hybrid format built once, on the GPU, before the timed region.  The default workload is the
+power-law R-MAT matrix of scale 21 (edge factor 32, symmetrised, self loops, GCN-normalised),
+F = 128 fp16 features, generated from a fixed seed on the device (synthetic stand-in for the
+SuiteSparse graphs the reference is benchmarked on).  With N > 1 (launched under
+torch.distributed.run) the row windows are cut into N nnz-balanced ranges, one per rank, B is
+replicated and no collective runs in the data path; timing is CUDA events, max over ranks.
+
+One JSON line is printed by rank 0:
+  value ....... whole-job GFLOP/s with every input resident in HBM (kept nnz = nnz the format stores)
+  e2e ......... the same metric through the host-buffer C-ABI call (trs_resident_forward): B copied
+                from pinned host memory and C copied back inside the timed region, every step
+  roofline .... algorithmic bytes of one step / its device time, against the measured HBM peak
+  cpu_baseline  torch.sparse CSR fp32 matmul on the host cores (N = 1 only), same matrix
+
+--impl reference times that CPU operator alone (the reference has no CPU SpMM of its own; its
+tests' oracle operator is the stand-in) and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "tr-spmm_zzx_b200"))
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: (generator, kwargs, F)
+    "rmat21": ("rmat_graph", dict(scale=21, edge_factor=32, seed=0), 128),
+    "rmat20": ("rmat_graph", dict(scale=20, edge_factor=16, seed=0), 128),
+    "rmat18": ("rmat_graph", dict(scale=18, edge_factor=32, seed=0), 128),
+    "rmat16": ("rmat_graph", dict(scale=16, edge_factor=32, seed=0), 128),
+    "clustered": ("clustered_graph", dict(n=262144, community=128, intra=24, glob=4, seed=0), 128),
+    "uniform": ("uniform_graph", dict(n=4096, per_row=16, seed=0), 64),
+}
+DESCRIPTIONS = {
+    "rmat21": "R-MAT scale 21, edge factor 32, a=.57 b=c=.19 d=.05, symmetrised, dedup, self loops, GCN norm",
+    "rmat20": "R-MAT scale 20, edge factor 16 (GCN config matrix)",
+    "rmat18": "R-MAT scale 18, edge factor 32 (reduced-size probe)",
+    "rmat16": "R-MAT scale 16, edge factor 32 (profiling case)",
+    "clustered": "stochastic-block graph N=262144, 2048 communities of 128, 24 intra + 4 global + self",
+    "uniform": "uniform N=4096, 16 distinct columns per row + self",
+}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()  # our own child, by handle
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self):
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0])); mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(mhz), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def make_matrix(workload, device):
+    from trspmm import graphs
+    gen, kw, F = WORKLOADS[workload]
+    rp, col, val = getattr(graphs, gen)(device=device, **kw)
+    return rp, col, val, F
+
+
+def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):
+    """Canonical-CSR traffic of one SpMM: fp16 value + int32 column per entry, row pointers,
+    every B row once, every C element once."""
+    return nnz * 6 + (n_rows + 1) * 4 + n_cols * F * 2 + n_rows * F * out_bytes
+
+
+def cpu_spmm_time(rp, col, val, B, reps):
+    """torch.sparse CSR fp32 matmul on all host threads; median seconds of `reps` runs after 1 warm-up."""
+    from oracle import oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    rp, col, val, B = rp.cpu(), col.cpu(), val.cpu(), B.cpu()
+    A = torch.sparse_csr_tensor(rp.long(), col.long(), val.float().half().float(), (rp.numel() - 1, B.shape[0]))
+    Bf = B.float()
+    torch.sparse.mm(A, Bf)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        torch.sparse.mm(A, Bf)
+        ts.append(time.perf_counter() - t0)
+    del O
+    return statistics.median(ts)
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle operator (torch.sparse CSR matmul) on the host cores, whole matrix."""
+    if rank != 0:
+        return
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    rp, col, val, F = make_matrix(args.workload, dev)
+    n = rp.numel() - 1
+    nnz = col.numel()
+    B = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
+    rp, col, val, B = rp.cpu(), col.cpu(), val.cpu(), B.cpu()
+    torch.set_num_threads(os.cpu_count() or 1)
+    A = torch.sparse_csr_tensor(rp.long(), col.long(), val.float().half().float(), (n, n))
+    Bf = B.float()
+    t0 = time.perf_counter()
+    torch.sparse.mm(A, Bf)  # untimed first touch, also sizes the sample
+    t_full = time.perf_counter() - t0
+    sample = "whole matrix, all nnz (no dropped entries on the CPU path)"
+    budget = 150.0
+    if t_full * (args.steps + args.warmup) > budget:
+        # bounded sample: every s-th block of 4096 rows (all columns), so hubs and tail both appear
+        s_every = int(t_full * (args.steps + args.warmup) / budget) + 1
+        blocks = torch.arange(0, (n + 4095) // 4096, s_every)
+        rows = (blocks[:, None] * 4096 + torch.arange(4096)[None, :]).reshape(-1)
+        rows = rows[rows < n]
+        cnt = (rp[1:] - rp[:-1]).long()[rows]
+        starts = rp.long()[rows]
+        sub_rp = torch.zeros(rows.numel() + 1, dtype=torch.int64)
+        sub_rp[1:] = torch.cumsum(cnt, 0)
+        ent = torch.repeat_interleave(starts - sub_rp[:-1], cnt) + torch.arange(int(sub_rp[-1]))
+        A = torch.sparse_csr_tensor(sub_rp, col.long()[ent], val.float()[ent].half().float(), (rows.numel(), n))
+        nnz = int(sub_rp[-1])
+        sample = f"every {s_every}th block of 4096 rows ({rows.numel()} rows, {nnz} nnz), all columns"
+    for _ in range(args.warmup):
+        torch.sparse.mm(A, Bf)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch.sparse.mm(A, Bf)
+    sec = (time.perf_counter() - t0) / args.steps
+    gflops = 2.0 * nnz * F / sec / 1e9
+    line = {
+        "impl": "reference", "metric": "SpMM GFLOP/s (2*nnz*F)", "value": gflops, "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "description": DESCRIPTIONS[args.workload], "n_rows": n, "nnz": nnz,
+                   "F": F, "operator": "torch.sparse.mm CSR fp32 x dense fp32 on the host cores"},
+        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from trspmm import ResidentSpmm, SpmmPlan, build_format, shard
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    rp, col, val, F = make_matrix(args.workload, dev)
+    n = rp.numel() - 1
+    nnz_total = col.numel()
+    if world > 1:
+        (r0, r1), (rp_l, col_l, val_l) = shard.shard_for_rank(rp, col, val, rank, world)
+    else:
+        r0, r1, rp_l, col_l, val_l = 0, n, rp, col, val
+    m_local = r1 - r0
+    fmt, st = build_format(rp_l, col_l, val_l)
+    kept_local = st["nnz"] - st["dropped_nnz"]
+    B = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
+    plan = SpmmPlan(fmt, max(m_local, 1), n, validate=True)
+    out = torch.empty((max(m_local, 1), F), dtype=torch.float16, device=dev)
+    cpu_inputs = (rp.cpu(), col.cpu(), val.cpu()) if (world == 1 and not args.no_cpu) else None
+    del rp, col, val
+    torch.cuda.empty_cache()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        plan.run(B, out=out)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            plan.run(B, out=out)
+        e1.record()
+        sync_all()
+    ms = e0.elapsed_time(e1) / args.steps
+    status = plan.status()
+
+    # ---- e2e through the host-buffer C-ABI entry: B from pinned host memory, C back to the host
+    res = ResidentSpmm(fmt, max(m_local, 1), n, 16, F)
+    B_host = B.cpu().pin_memory()
+    C_host = torch.empty((max(m_local, 1), F), dtype=torch.float16).pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
+    res.forward(B_host, C_host)
+    sync_all()
+    t0 = time.perf_counter()
+    h2d = d2h = 0.0
+    for _ in range(e2e_steps):
+        _, tm = res.forward(B_host, C_host)  # blocks until C is on the host
+        h2d += tm.h2d_ms; d2h += tm.d2h_ms
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    res.close()
+
+    kept = torch.tensor([float(kept_local), ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        tot = kept.clone()
+        dist.all_reduce(tot[0:1], op=dist.ReduceOp.SUM)
+        dist.all_reduce(tot[1:3], op=dist.ReduceOp.MAX)
+        kept_total, ms, e2e_ms = float(tot[0]), float(tot[1]), float(tot[2])
+    else:
+        kept_total = float(kept_local)
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        alg = algorithmic_bytes(kept_total, n, n, F, 2)  # whole job; B counted once per GPU below
+        alg_job = alg + (world - 1) * n * F * 2          # every rank streams its own replica of B
+        alg_rank = algorithmic_bytes(kept_local, m_local, n, F, 2)
+        achieved = alg_rank / (ms * 1e-3) / 1e9
+        line = {
+            "metric": "SpMM GFLOP/s (2*nnz*F)", "value": 2.0 * kept_total * F / (ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "description": DESCRIPTIONS[args.workload], "n_rows": n,
+                       "nnz": nnz_total, "kept_nnz": int(kept_total), "F": F, "out": "f16",
+                       "parallelism": f"row-window shards x{world}, B replicated, no collective",
+                       "l2": "inputs larger than L2 (no flush)" if n * F * 2 > 126e6 else "B fits L2",
+                       "build_ms_rank0": st["build_ms"], "tiles_rank0": st["tiles"], "tc_blocks_rank0": st["tc_blocks"]},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "algorithmic_bytes_per_step_rank0": alg_rank,
+                         "algorithmic_bytes_per_step_job": alg_job, "traffic": None, "kernel": "k_window_spmm"},
+            "e2e": {"value": 2.0 * kept_total * F / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": n * F * 2, "d2h_bytes_per_step": max(m_local, 1) * F * 2,
+                    "h2d_ms": h2d / e2e_steps, "d2h_ms": d2h / e2e_steps,
+                    "call": "trs_resident_forward (format resident, B host->device, C device->host)"},
+            "gpu_launches": plan.launches * args.steps,
+            "clocks": clocks.summary(), "kernel_status": status,
+        }
+        if cpu_inputs is not None:
+            reps = 3
+            sec = cpu_spmm_time(*cpu_inputs, B, reps)
+            line["cpu_baseline"] = {"value": 2.0 * nnz_total * F / sec / 1e9, "unit": "GFLOP/s", "cores": os.cpu_count(),
+                                    "kind": "port", "sample": f"whole matrix, median of {reps} runs of torch.sparse.mm "
+                                    f"CSR fp32 ({sec * 1e3:.0f} ms each)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="rmat21", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

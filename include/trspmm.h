@@ -122,6 +122,10 @@ int trs_spmm_forward_host(const trs_format* host_format, const trs_half* rhs_hos
 typedef struct trs_resident trs_resident;
 int trs_resident_create(const trs_format* host_format, int mOri, int kOri, int window,
                         int max_dimN, trs_resident** out);
+/* Same, over format arrays that already live on the device (e.g. a builder's output); the
+ * arrays stay caller-owned and must outlive the handle. */
+int trs_resident_create_device(const trs_format* dev_format, int mOri, int kOri, int window,
+                               int max_dimN, trs_resident** out);
 int trs_resident_forward(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN,
                          int out_dtype, trs_timing* timing);
 int trs_resident_destroy(trs_resident* h);

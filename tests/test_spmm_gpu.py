@@ -176,3 +176,17 @@ def test_ragged_last_window_and_empty_rows():
     dst = torch.full((64, 16), 7.0, device="cuda")
     plan.run(torch.randn(64, 16).half().cuda(), out=dst)
     assert float(dst.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("F", [32, 64, 128, 256, 40])
+def test_bulk_copy_kernel_variant(F, monkeypatch):
+    """The warp-specialised bulk-copy (TMA) kernel, selected with TRS_SPMM_KERNEL=bulk, computes the
+    same product; its bounded mbarrier waits report no timeout."""
+    monkeypatch.setenv("TRS_SPMM_KERNEL", "bulk")
+    monkeypatch.setenv("TRS_CHUNK_STEPS", "16")
+    arrays, n = _golden("clustered_n512")
+    B = torch.randn(n, F, generator=torch.Generator().manual_seed(F)).half()
+    ref = O.spmm_from_format(arrays, B, n)
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    _check(plan.run(B.cuda(), out_dtype=torch.float32), plan.run(B.cuda(), out_dtype=torch.float16), ref)
+    assert plan.status() == 0

@@ -185,6 +185,30 @@ extern "C" int trs_resident_create(const trs_format* host_format, int mOri, int 
     return TRS_OK;
 }
 
+extern "C" int trs_resident_create_device(const trs_format* dev_format, int mOri, int kOri, int window, int max_dimN,
+                                          trs_resident** out) {
+    if (!dev_format || !out || max_dimN <= 0) return TRS_E_ARG;
+    *out = nullptr;
+    if (mOri <= 0 || kOri <= 0) return TRS_E_ARG;
+    if (window <= 0 || window > 16) return TRS_E_WINDOW;
+    if (trs_device_count() == 0) return TRS_E_NO_DEVICE;
+    trs_resident* h = new trs_resident();
+    h->dev = *dev_format;
+    int rc = trs_spmm_plan_create(&h->dev, mOri, kOri, window, 1, nullptr, &h->plan);
+    if (!rc) rc = trs_spmm_workspace_bytes(h->plan, max_dimN, &h->ws_bytes);
+    if (!rc) rc = h->up.raw<unsigned char>(h->ws_bytes, (unsigned char**)&h->d_ws);
+    if (!rc) rc = h->up.raw<trs_half>((size_t)kOri * max_dimN, &h->d_rhs);
+    if (!rc) rc = h->up.raw<unsigned char>((size_t)mOri * max_dimN * sizeof(float), (unsigned char**)&h->d_out);
+    if (!rc) {
+        cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) rc = (int)e;
+    }
+    if (rc) { trs_resident_destroy(h); return rc; }
+    h->m_rows = mOri; h->k_cols = kOri; h->max_dim = max_dimN;
+    *out = h;
+    return TRS_OK;
+}
+
 extern "C" int trs_resident_destroy(trs_resident* h) {
     if (!h) return TRS_OK;
     if (h->plan) trs_spmm_plan_destroy(h->plan);

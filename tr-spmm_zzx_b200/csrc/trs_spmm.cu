@@ -748,9 +748,11 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     if (e != cudaSuccess) { trs_spmm_plan_destroy(p); return (int)e; }
     const uintptr_t align_or = (uintptr_t)f.s_tile_column | (uintptr_t)f.s_packed_a | (uintptr_t)f.s_packed_meta |
                                (uintptr_t)f.t_column;
-    p->bulk_ok = (align_or & 15) == 0;
+    // The warp-specialised bulk-copy kernel is opt-in (TRS_SPMM_KERNEL=bulk): measured on B200 it
+    // is slower than the cp.async kernel because 256-byte bulk copies cost ~7 cycles each in the
+    // copy engine; it is kept for wider rows and as the structure a gather4 tensor copy would use.
     const char* kv = getenv("TRS_SPMM_KERNEL");
-    if (kv && strcmp(kv, "cpasync") == 0) p->bulk_ok = false;
+    p->bulk_ok = (align_or & 15) == 0 && kv && strcmp(kv, "bulk") == 0;
     *out_plan = p;
     return TRS_OK;
 }

@@ -76,6 +76,8 @@ def load():
     lib.trs_spmm_launches.argtypes = [vp]
     lib.trs_spmm_forward_host.argtypes = [C.POINTER(TrsFormat), vp, vp, i32, i32, i32, i32, i32, C.POINTER(TrsTiming)]
     lib.trs_resident_create.argtypes = [C.POINTER(TrsFormat), i32, i32, i32, i32, C.POINTER(vp)]
+    lib.trs_resident_create_device.argtypes = [C.POINTER(TrsFormat), i32, i32, i32, i32, C.POINTER(vp)]
+    lib.trs_resident_create_device.restype = i32
     lib.trs_resident_forward.argtypes = [vp, vp, vp, i32, i32, C.POINTER(TrsTiming)]
     lib.trs_resident_destroy.argtypes = [vp]
     lib.trs_sptc_unpacked_forward_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32,

@@ -113,11 +113,18 @@ class ResidentSpmm:
 
     def __init__(self, fmt: Format, mOri: int, kOri: int, window: int = 16, max_dimN: int = 256):
         self.lib = _lib.load()
-        self._keep = _cpu_format(fmt)
         self._handle = C.c_void_p()
         self.mOri, self.kOri, self.max_dimN = mOri, kOri, max_dimN
-        cf = self._keep.c_struct()
-        _lib.check(self.lib.trs_resident_create(C.byref(cf), mOri, kOri, window, max_dimN, C.byref(self._handle)))
+        if fmt.device.type == "cuda":  # e.g. straight from the GPU builder: no host round trip
+            self._keep = fmt.half_values().contiguous()
+            cf = self._keep.c_struct()
+            with torch.cuda.device(fmt.device):
+                _lib.check(self.lib.trs_resident_create_device(C.byref(cf), mOri, kOri, window, max_dimN,
+                                                               C.byref(self._handle)))
+        else:
+            self._keep = _cpu_format(fmt)
+            cf = self._keep.c_struct()
+            _lib.check(self.lib.trs_resident_create(C.byref(cf), mOri, kOri, window, max_dimN, C.byref(self._handle)))
 
     def forward(self, rhs: torch.Tensor, out: torch.Tensor):
         if rhs.device.type != "cpu" or out.device.type != "cpu":
