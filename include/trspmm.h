@@ -105,6 +105,22 @@ int trs_spmm_run(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, i
 /* Health word of the plan's kernels: 0, or non-zero when a bounded pipeline wait inside a kernel
  * gave up (the affected call's output is then incomplete).  Synchronises the device. */
 int trs_spmm_status(const trs_spmm_plan* plan, int* status);
+/* trs_spmm_run for callers that can neither allocate device memory nor be handed any: hosts that
+ * gave the whole device to their own memory pool at start-up, and latency-critical loops where
+ * cudaMalloc / cudaFree would stall every stream.  This entry has no counterpart in the
+ * reference.  It runs the same kernels as trs_spmm_run, keeping the partial sums of split
+ * windows in a fixed array inside the library (TRS_STATIC_SCRATCH_BYTES per GPU, held from
+ * library load to process exit) and allocates nothing, on the host or the device.
+ *   - returns TRS_E_LIMIT when the plan needs more scratch for this F than the array holds
+ *     (trs_spmm_workspace_bytes tells the need); nothing is launched then;
+ *   - the first call on each device looks up the array's device address; make that call before
+ *     any stream capture starts on that device;
+ *   - all calls on a device share the one array: calls whose kernels may overlap on the GPU
+ *     (different streams) race on it, so keep them ordered.  No clearing is needed between
+ *     calls: every slot a call reads is fully written by that call first. */
+#define TRS_STATIC_SCRATCH_BYTES (8u << 20)
+int trs_spmm_run_static(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
+                        void* stream);
 /* Number of kernels one trs_spmm_run launches (1, or 2 when some window is split). */
 int trs_spmm_launches(const trs_spmm_plan* plan);
 

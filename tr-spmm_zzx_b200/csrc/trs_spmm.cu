@@ -18,6 +18,8 @@
 
 #include <string.h>
 
+#include <mutex>
+
 #include "trs_common.cuh"
 
 namespace trs {
@@ -836,4 +838,49 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
         TRS_LAUNCH_CHECK();
     }
     return TRS_OK;
+}
+
+// ----------------------------------------------------------------------------------------------
+// SpMM without any allocation: partial sums in a fixed, library-owned device array
+// ----------------------------------------------------------------------------------------------
+// Some hosts cannot give this library scratch memory at call time: applications that hand the
+// whole device memory to their own pool at start-up (a later cudaMalloc from a plug-in fails or
+// fragments that pool) and latency-critical loops in which cudaMalloc / cudaFree would stall
+// every stream of the device.  For them trs_spmm_run_static runs the same kernels as
+// trs_spmm_run, with the partial sums of split windows kept in the array below instead of a
+// caller-provided workspace.  Every GPU that loads the library holds these bytes until exit.
+//
+// In host code the array's name is only a stand-in for the symbol; the device address is asked
+// for once per device (cudaGetSymbolAddress with that device current) and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[TRS_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+bool g_static_scratch_ready[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+}  // namespace
+
+extern "C" int trs_spmm_run_static(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype,
+                                   void* stream) {
+    if (!p || !B || !C || F <= 0) return TRS_E_ARG;
+    const size_t need = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
+    if (need > (size_t)TRS_STATIC_SCRATCH_BYTES) return TRS_E_LIMIT;
+    int dev = -1;
+    TRS_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return TRS_E_LIMIT;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_ready[dev]) {  // first call on this device: look the symbol up
+            void* ptr = nullptr;
+            TRS_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+            g_static_scratch_ptr[dev] = ptr;
+            g_static_scratch_ready[dev] = true;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    // Nothing in the array has to start at zero: every slot a call reads is first written in
+    // full by that call's window kernel.
+    return trs_spmm_run(p, B, C, F, out_dtype, scratch, (size_t)TRS_STATIC_SCRATCH_BYTES, stream);
 }

@@ -74,6 +74,22 @@ class SpmmPlan:
                                              ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(self.device)))
         return out
 
+    def run_static(self, B: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """trs_spmm_run_static: the same product with the partial sums of split windows kept in
+        the library's fixed device array, for callers that may not allocate device memory (the
+        whole device belongs to their own pool, or an allocation would stall their streams).
+        `out` must be given: this path allocates nothing, here or in the library.  Raises
+        TrsError(-10) when the plan needs more scratch than the fixed array holds.  Calls on one
+        device share the array, so do not let two of them overlap on the GPU."""
+        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
+            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
+        if out.shape != (self.m_rows, B.shape[1]) or not out.is_contiguous() or out.device != self.device:
+            raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.trs_spmm_run_static(self._handle, B.data_ptr(), out.data_ptr(), B.shape[1],
+                                                    _out_code(out.dtype), _lib.current_stream_ptr(self.device)))
+        return out
+
     def close(self):
         if getattr(self, "_handle", None) is not None and self._handle:
             self.lib.trs_spmm_plan_destroy(self._handle)
