@@ -1,0 +1,134 @@
+"""Row-window sharding (host logic) on CPU, including a world_size-2 gloo run.
+
+The property that makes the single-SpMM path collective-free: every window is built and
+multiplied independently, so a rank's format arrays are the matching segments of the unsharded
+arrays and concatenating the per-rank results reproduces the unsharded result bit for bit.
+The CPU oracle stands in for the GPU operators here (no GPU in this test)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle as O
+from trspmm import graphs, shard
+
+
+def test_cuts_are_window_aligned_and_balanced():
+    rp, col, val = graphs.rmat_graph(12, 16, seed=3)
+    n = rp.numel() - 1
+    for parts in (1, 2, 3, 8):
+        cuts = shard.balanced_window_cuts(rp, parts)
+        assert cuts[0] == 0 and cuts[-1] == n and len(cuts) == parts + 1
+        assert all(c % 16 == 0 for c in cuts[:-1]) and cuts == sorted(cuts)
+        loads = [int(rp[b] - rp[a]) for a, b in zip(cuts[:-1], cuts[1:])]
+        heaviest_window = int((rp[16::16] - rp[:-16:16]).max())
+        assert max(loads) <= col.numel() / parts + heaviest_window
+    # ragged row count and more parts than windows
+    rp2, _, _ = graphs.uniform_graph(100, 3, seed=1)
+    cuts = shard.balanced_window_cuts(rp2, 16)
+    assert cuts[0] == 0 and cuts[-1] == 100 and cuts == sorted(cuts)
+
+
+def test_shard_formats_are_segments_of_the_full_format():
+    rp, col, val = graphs.clustered_graph(1024, 64, 12, 2, seed=2)
+    full, _ = O.build_format(rp, col, val)
+    named = dict(zip(O.FORMAT_NAMES, full))
+    cuts = shard.balanced_window_cuts(rp, 3)
+    g0 = t0 = 0
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        rp_l, col_l, val_l = shard.slice_csr(rp, col, val, a, b)
+        part, _ = O.build_format(rp_l, col_l, val_l)
+        p = dict(zip(O.FORMAT_NAMES, part))
+        G, T = p["s_column"].shape[0], p["s_tile_column"].shape[0]
+        assert torch.equal(p["s_column"], named["s_column"][g0:g0 + G])
+        assert torch.equal(p["s_value"], named["s_value"][g0:g0 + G])
+        assert torch.equal(p["s_packed_a"], named["s_packed_a"][t0:t0 + T])
+        assert torch.equal(p["s_packed_meta"], named["s_packed_meta"][t0:t0 + T])
+        assert torch.equal(p["s_tile_column"], named["s_tile_column"][t0:t0 + T])
+        w0 = a // 16
+        assert torch.equal(p["s_offset"], named["s_offset"][w0:w0 + p["s_offset"].numel()] - g0)
+        g0 += G
+        t0 += T
+    assert g0 == named["s_column"].shape[0] and t0 == named["s_tile_column"].shape[0]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rp, col, val = graphs.rmat_graph(10, 8, seed=7)  # same seed on every rank
+        n = rp.numel() - 1
+        B = torch.randn(n, 16, generator=torch.Generator().manual_seed(0)).half()
+        (r0, r1), (rp_l, col_l, val_l) = shard.shard_for_rank(rp, col, val, rank, world)
+        fmt, _ = O.build_format(rp_l, col_l, val_l)
+        mine = O.spmm_from_format(fmt, B, r1 - r0)
+        # gather the row blocks: every rank contributes a different number of rows
+        cuts = shard.balanced_window_cuts(rp, world)
+        full = torch.zeros(n, 16)
+        full[r0:r1] = mine
+        for src in range(world):
+            dist.broadcast(full[cuts[src]:cuts[src + 1]], src=src)
+        if rank == 0:
+            whole, _ = O.build_format(rp, col, val)
+            q.put(bool(torch.equal(full, O.spmm_from_format(whole, B, n))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reassemble_the_unsharded_result():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+        assert p.exitcode == 0
+    assert q.get(timeout=10) is True
+
+
+def _failing_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    try:
+        if rank == 1:
+            raise RuntimeError("injected host-side failure before the collective")
+        try:
+            t = torch.zeros(4)
+            dist.broadcast(t, src=1)  # the peer never joins
+            q.put("no error")
+        except Exception as exc:  # the survivor sees an error instead of hanging
+            q.put("error: " + type(exc).__name__)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_failure_is_seen_on_the_host():
+    """Failure detection without touching a GPU: a rank raises before the collective, the other
+    rank's collective ends with an error within the process-group timeout."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    assert procs[1].exitcode != 0
+    assert q.get(timeout=10).startswith("error")
