@@ -102,6 +102,12 @@ int trs_spmm_workspace_bytes(const trs_spmm_plan* plan, int F, size_t* bytes);
  * needed), fp32 or fp16 per out_dtype.  Asynchronous on `stream`; allocates nothing. */
 int trs_spmm_run(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* Same with an epilogue fused into the single write of C.  TRS_EPILOGUE_RELU: C = max(A'B, 0), the
+ * activation of a GCN layer H = ReLU(A (X W)) (no layer code exists in the reference; the SpMM it
+ * would call is mGCN_online.cpp:760). */
+#define TRS_EPILOGUE_RELU 1
+int trs_spmm_run_ex(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype, int flags,
+                    void* workspace, size_t workspace_bytes, void* stream);
 /* Health word of the plan's kernels: 0, or non-zero when a bounded pipeline wait inside a kernel
  * gave up (the affected call's output is then incomplete).  Synchronises the device. */
 int trs_spmm_status(const trs_spmm_plan* plan, int* status);

@@ -67,6 +67,7 @@ struct KernelArgs {
     const unsigned char* zeros;    // 512 zero bytes: source of padded (-1) columns / absent blocks
     int* status;                   // device word: non-zero after a pipeline wait gave up
     int m_rows, k_cols, window, F, out_half;
+    int relu;                      // 1: C = max(A'B, 0) (GCN layer epilogue)
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -201,6 +202,12 @@ __device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, 
         }
         return;
     }
+    if (a.relu) {
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][i] = fmaxf(acc[n][i], 0.f);
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int lr = g + 8 * h;
@@ -211,14 +218,14 @@ __device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, 
             const int f = fcol + n * 8;
             if (a.out_half) {
                 __half* d = (__half*)a.C + (size_t)row * F + f;
-                if (f + 1 < a.F && (a.F & 1) == 0) *(__half2*)d = __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]);
+                if (f + 1 < a.F && (a.F & 1) == 0) { const __half2 hv = __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]); __stcs((unsigned int*)d, *(const unsigned int*)&hv); }
                 else {
                     if (f < a.F) d[0] = __float2half_rn(acc[n][2 * h]);
                     if (f + 1 < a.F) d[1] = __float2half_rn(acc[n][2 * h + 1]);
                 }
             } else {
                 float* d = (float*)a.C + (size_t)row * F + f;
-                if (f + 1 < a.F && (a.F & 1) == 0) *(float2*)d = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+                if (f + 1 < a.F && (a.F & 1) == 0) __stcs((float2*)d, make_float2(acc[n][2 * h], acc[n][2 * h + 1]));
                 else {
                     if (f < a.F) d[0] = acc[n][2 * h];
                     if (f + 1 < a.F) d[1] = acc[n][2 * h + 1];
@@ -390,6 +397,143 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
     }
     cp_async_wait<0>();
 
+    finish_item(acc, it, a, fbase, wid, g, t);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Lean variant of the cp.async kernel for the aligned case (F % 8 == 0, 16-byte aligned arrays).
+// Same pipeline and numerics as k_window_spmm<WARPS, true>; what changes is the instruction
+// count of the inner loop, which ncu showed to be the limiter (81 % issue-active, 131 warp
+// instructions per k-step):
+//   * stage and ring slots are compile-time constants (loop unrolled by the stage count),
+//   * source addresses are one 32-bit multiply-add (16-byte units) plus one wide add,
+//   * the dense TC operand comes pre-expanded from the plan through the same cp.async pipeline
+//     (no bitmap decoding in the loop),
+//   * all shared-memory addresses are hoisted out of the loop.
+// ----------------------------------------------------------------------------------------------
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArgs a) {
+    using T = Tile<WARPS>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int fbase = blockIdx.y * T::FS;
+
+    const Item it = a.items[blockIdx.x];
+    const int nsteps = it.step_end - it.step_begin;
+    const int nsparse = min(max(it.ntiles - it.step_begin, 0), nsteps);  // steps [0, nsparse) are packed tiles
+
+    const uint32_t smem0 = smem_u32(smem);
+    const uint32_t ring0 = smem0 + T::STAGE * kStages;
+    const int* ring = (const int*)(smem + T::STAGE * kStages);
+
+    const int ch = tid % T::CPR, row0 = tid / T::CPR;
+    const uint32_t pitch16 = (uint32_t)a.F >> 3;             // 16-byte units per B row
+    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;    // this thread's chunk inside a row
+    const bool fin = fbase + ch * 8 < a.F;
+    const uint4* Bq = (const uint4*)a.B;
+    const uint32_t dst0 = smem0 + row0 * T::ROWB + ch * 16;
+    const int mtx = lane >> 3;
+    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + (wid * 32 + (mtx >> 1) * 8) * 2;
+    const unsigned char* a_lane = smem + T::BBYTES;          // + stage * STAGE
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    auto issue_idx = [&](int m) {
+        if (tid < 4 && m < nsteps) {
+            const int s = it.step_begin + m;
+            const uint32_t dst = ring0 + (m & (kIdxRing - 1)) * 64 + tid * 16;
+            if (s < it.ntiles) {
+                cp_async16(dst, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + tid * 4, 16);
+            } else {
+                const int b = it.blk0 + 2 * (s - it.ntiles) + (tid >> 1);
+                if (b < it.blk_end) cp_async16(dst, a.f.t_column + (size_t)b * 8 + (tid & 1) * 4, 16);
+                else *(int4*)(smem + T::STAGE * kStages + (m & (kIdxRing - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
+            }
+        }
+    };
+
+    auto issue = [&](int j, int stage) {
+        const int* cols = ring + (j & (kIdxRing - 1)) * 16;
+        const int c0 = cols[row0], c1 = cols[row0 + 8];
+        const uint32_t o0 = (uint32_t)max(c0, 0) * pitch16 + chunk16;
+        const uint32_t o1 = (uint32_t)max(c1, 0) * pitch16 + chunk16;
+        cp_async16(dst0 + stage * T::STAGE, Bq + o0, (c0 >= 0 && fin) ? 16 : 0);
+        cp_async16(dst0 + stage * T::STAGE + 8 * T::ROWB, Bq + o1, (c1 >= 0 && fin) ? 16 : 0);
+        if (tid < 32) {  // A operand: warp 0
+            const int s = it.step_begin + j;
+            const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + tid * 16;
+            if (s < it.ntiles) {
+                const size_t tile = (size_t)(it.tile0 + s);
+                if (tid < 16) cp_async16(adst, a.f.s_packed_a + tile * 64 + tid * 4, 16);
+                else if (tid < 18) cp_async16(adst, a.f.s_packed_meta + tile * 8 + (tid - 16) * 4, 16);
+            } else {
+                const int b = it.blk0 + 2 * (s - it.ntiles) + (tid >> 4);
+                const bool live = b < it.blk_end;
+                cp_async16(adst, a.tc_dense + (size_t)(live ? b : it.blk0) * 128 + (tid & 15) * 8, live ? 16 : 0);
+            }
+        }
+    };
+
+    auto compute = [&](int j, int stage) {
+        const unsigned char* as = a_lane + stage * T::STAGE;
+        const uint32_t baddr = boff + stage * T::STAGE;
+        if (j < nsparse) {
+            const uint2 av = *(const uint2*)(as + lane * 8);
+            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+            }
+        } else {
+            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
+            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
+            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
+            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+    };
+
+#pragma unroll
+    for (int m = 0; m < kIdxAhead; ++m) issue_idx(m);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kStages - 1; ++j) {
+        if (j < nsteps) issue(j, j);
+        cp_async_commit();
+    }
+    for (int j0 = 0; j0 < nsteps; j0 += kStages) {
+#pragma unroll
+        for (int u = 0; u < kStages; ++u) {
+            const int j = j0 + u;
+            if (j < nsteps) {
+                cp_async_wait<kStages - 2>();
+                __syncthreads();
+                issue_idx(j + kIdxAhead);
+                if (j + kStages - 1 < nsteps) issue(j + kStages - 1, (u + kStages - 1) % kStages);
+                cp_async_commit();
+                compute(j, u);
+            }
+        }
+    }
+    cp_async_wait<0>();
     finish_item(acc, it, a, fbase, wid, g, t);
 }
 
@@ -575,7 +719,7 @@ __global__ void k_expand_tc(const long long* __restrict__ t_binary, const int* _
 
 // Adds the partial sums of a split window in slot order and writes its 16 rows of C.
 __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __restrict__ scratch, void* C, int F,
-                               int m_rows, int window, int out_half) {
+                               int m_rows, int window, int out_half, int relu) {
     const Heavy h = heavy[blockIdx.x];
     const int per = 16 * F;
     for (int i = threadIdx.x; i < per; i += blockDim.x) {
@@ -584,6 +728,7 @@ __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __r
         if (lr >= window || row >= m_rows) continue;
         float s = 0.f;
         for (int sl = h.slot_begin; sl < h.slot_end; ++sl) s += scratch[(size_t)sl * per + i];
+        if (relu) s = fmaxf(s, 0.f);
         if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
         else ((float*)C)[(size_t)row * F + f] = s;
     }
@@ -606,7 +751,8 @@ struct trs_spmm_plan {
     DevBuf<__half> tc_dense;          // expanded TC blocks for the bulk-copy kernel
     DevBuf<unsigned char> zeros;      // 512 zero bytes + the status word behind them
     int n_items, n_heavy, n_slots;
-    bool bulk_ok;                     // format arrays are 16-byte aligned: bulk-copy kernel usable
+    bool bulk_ok;                     // bulk-copy kernel requested and usable
+    bool arrays_aligned;              // index / tile arrays are 16-byte aligned
 };
 
 static int env_int(const char* name, int dflt) {
@@ -754,7 +900,8 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     // is slower than the cp.async kernel because 256-byte bulk copies cost ~7 cycles each in the
     // copy engine; it is kept for wider rows and as the structure a gather4 tensor copy would use.
     const char* kv = getenv("TRS_SPMM_KERNEL");
-    p->bulk_ok = (align_or & 15) == 0 && kv && strcmp(kv, "bulk") == 0;
+    p->arrays_aligned = (align_or & 15) == 0;
+    p->bulk_ok = p->arrays_aligned && kv && strcmp(kv, "bulk") == 0;
     *out_plan = p;
     return TRS_OK;
 }
@@ -796,11 +943,15 @@ static int launch_bulk_kernel(const KernelArgs& a, int n_items, cudaStream_t st)
 }
 
 template <int WARPS>
-static int launch_window_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
+static int launch_window_kernel(const KernelArgs& a, int n_items, bool lean_ok, cudaStream_t st) {
     using T = Tile<WARPS>;
     const bool aligned = (a.F % 8 == 0) && (((uintptr_t)a.B & 15) == 0);
     dim3 grid(n_items, ceil_div(a.F, T::FS));
-    if (aligned) {
+    static const bool use_lean = [] { const char* v = getenv("TRS_SPMM_KERNEL"); return !(v && strcmp(v, "cpasync_v1") == 0); }();
+    if (aligned && lean_ok && use_lean) {
+        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+        k_window_spmm_lean<WARPS><<<grid, T::THREADS, T::SMEM, st>>>(a);
+    } else if (aligned) {
         TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
         k_window_spmm<WARPS, true><<<grid, T::THREADS, T::SMEM, st>>>(a);
     } else {
@@ -813,7 +964,13 @@ static int launch_window_kernel(const KernelArgs& a, int n_items, cudaStream_t s
 
 extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, void* workspace,
                             size_t workspace_bytes, void* stream) {
+    return trs_spmm_run_ex(p, B, C, F, out_dtype, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
+                               void* workspace, size_t workspace_bytes, void* stream) {
     if (!p || !B || !C || F <= 0) return TRS_E_ARG;
+    if (flags & ~TRS_EPILOGUE_RELU) return TRS_E_ARG;
     if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
     size_t need = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
     if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
@@ -822,6 +979,7 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
     a.f = p->f; a.wr = p->wr; a.items = p->items.p;
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
+    a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
     a.tc_dense = p->tc_dense.p; a.zeros = p->zeros.p; a.status = (int*)(p->zeros.p + 512);
     int rc;
     const bool bulk = p->bulk_ok && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
@@ -829,12 +987,12 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
         if (F <= 32) rc = launch_bulk_kernel<1>(a, p->n_items, st);
         else if (F <= 64) rc = launch_bulk_kernel<2>(a, p->n_items, st);
         else rc = launch_bulk_kernel<4>(a, p->n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
-    } else if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, st);
-    else if (F <= 64) rc = launch_window_kernel<2>(a, p->n_items, st);
-    else rc = launch_window_kernel<4>(a, p->n_items, st);
+    } else if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, p->arrays_aligned, st);
+    else if (F <= 64) rc = launch_window_kernel<2>(a, p->n_items, p->arrays_aligned, st);
+    else rc = launch_window_kernel<4>(a, p->n_items, p->arrays_aligned, st);
     if (rc) return rc;
     if (p->n_heavy > 0) {
-        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half);
+        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half, a.relu);
         TRS_LAUNCH_CHECK();
     }
     return TRS_OK;

@@ -74,6 +74,8 @@ def load():
     lib.trs_spmm_workspace_bytes.argtypes = [vp, i32, C.POINTER(sz)]
     lib.trs_spmm_run.argtypes = [vp, vp, vp, i32, i32, vp, sz, vp]
     lib.trs_spmm_launches.argtypes = [vp]
+    lib.trs_spmm_run_ex.argtypes = [vp, vp, vp, i32, i32, i32, vp, sz, vp]
+    lib.trs_spmm_run_ex.restype = i32
     lib.trs_spmm_run_static.argtypes = [vp, vp, vp, i32, i32, vp]
     lib.trs_spmm_run_static.restype = i32
     lib.trs_spmm_forward_host.argtypes = [C.POINTER(TrsFormat), vp, vp, i32, i32, i32, i32, i32, C.POINTER(TrsTiming)]

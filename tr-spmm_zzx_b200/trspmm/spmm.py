@@ -55,7 +55,8 @@ class SpmmPlan:
     def launches(self) -> int:
         return self.lib.trs_spmm_launches(self._handle)
 
-    def run(self, B: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float16) -> torch.Tensor:
+    def run(self, B: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float16,
+            relu: bool = False) -> torch.Tensor:
         if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
             raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
         if B.shape[0] != self.k_cols:
@@ -70,8 +71,9 @@ class SpmmPlan:
             ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
             self._ws[F] = ws
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.trs_spmm_run(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
-                                             ws.data_ptr(), ws.numel(), _lib.current_stream_ptr(self.device)))
+            _lib.check(self.lib.trs_spmm_run_ex(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
+                                                1 if relu else 0, ws.data_ptr(), ws.numel(),
+                                                _lib.current_stream_ptr(self.device)))
         return out
 
     def run_static(self, B: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
