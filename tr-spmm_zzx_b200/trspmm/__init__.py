@@ -10,3 +10,5 @@ from .format import FORMAT_NAMES, Format  # noqa: F401
 from .spmm import SpmmPlan, spmm_forward_host, ResidentSpmm  # noqa: F401
 from .sddmm import sddmm  # noqa: F401
 from .builder import build_format  # noqa: F401
+from .gcn import ShardedGCN2  # noqa: F401
+from . import shard  # noqa: F401

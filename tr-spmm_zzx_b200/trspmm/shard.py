@@ -35,6 +35,38 @@ def balanced_window_cuts(rowptr: torch.Tensor, parts: int, window: int = 16):
     return cuts
 
 
+def cuts_from_window_costs(cost: torch.Tensor, parts: int, n_rows: int, window: int = 16):
+    """Row boundaries from a per-window cost vector (e.g. k-steps of the built format + a fixed
+    per-window overhead): contiguous window ranges of about equal total cost."""
+    W = cost.numel()
+    prefix = torch.zeros(W + 1, dtype=torch.float64, device=cost.device)
+    prefix[1:] = torch.cumsum(cost.double(), 0)
+    total = float(prefix[-1])
+    cuts = [0]
+    for k in range(1, parts):
+        w = int(torch.searchsorted(prefix, torch.tensor(total * k / parts, dtype=torch.float64, device=cost.device)))
+        w = min(max(w, cuts[-1] // window), W)
+        cuts.append(min(w * window, n_rows))
+    cuts.append(n_rows)
+    for i in range(1, len(cuts)):
+        cuts[i] = max(cuts[i], cuts[i - 1])
+    return cuts
+
+
+def window_steps(fmt, n_windows: int):
+    """k-steps per window of a built format: packed tiles + pairs of TC blocks."""
+    off = fmt.s_window_tile_offset
+    steps = (off[1:] - off[:-1]).to(torch.float32)
+    if steps.numel() < n_windows:
+        steps = torch.cat([steps, torch.zeros(n_windows - steps.numel(), device=steps.device)])
+    if fmt.t_window_row.numel():
+        blocks_per_part = (fmt.t_row_offset[1:] - fmt.t_row_offset[:-1]).to(torch.float32)
+        win = (fmt.t_window_row // 16).long()
+        blocks = torch.zeros(n_windows, device=steps.device).index_add_(0, win, blocks_per_part)
+        steps = steps + torch.ceil(blocks / 2)
+    return steps
+
+
 def slice_csr(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, r0: int, r1: int):
     """Rows [r0, r1) as their own CSR (row pointers rebased, global column ids kept)."""
     b, e = int(rowptr[r0]), int(rowptr[r1])
