@@ -206,6 +206,27 @@ int trs_build_format(trs_builder* b, trs_format* out, void* stream);
 /* the std::sort emulation used by the matching stage, run on the host (test hook) */
 int trs_debug_stdsort_order(const unsigned char* keys, int n, int* out, int* heap_sorts);
 
+/* ---- 2:4 matching statistics -------------------------------------------------------------------
+ * Deterministic GPU versions of the reference's statistic-only matchers; device CSR in, one
+ * record out (the reference returns the same numbers as a Python dict):
+ *   variant 0  matching_utils.match_2to4             (block_matching_window_para_dr.cpp:361-449)
+ *   variant 1  matching_utils_hash.match_2to4_hash   (block_matching_hash.cpp:373-441)
+ *   variant 2  matching_utils_bucket.match_2to4_bucket (block_matching_bucket.cpp:430-499)
+ * dense_threshold / t_max are used by variant 0 only (the others fix their thresholds). */
+typedef struct trs_match_stats {
+    int32_t total_rows, total_cols;
+    long long total_nnz;
+    double sparsity;
+    int32_t num_row_panels;
+    long long num_groups;        /* "num_sptc_groups" of variant 0 */
+    long long num_tc_blocks;     /* variant 0 only */
+    long long num_16x16_blocks, block_padding_groups, fine_fallback, coarse_fallback, fake_zeros;
+    long long tc_total_nnz, tc_block_count; /* variant 0 only */
+    int32_t tc_block_max_nnz, tc_block_min_nnz;
+} trs_match_stats;
+int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, int n_rows, int window,
+                      int dense_threshold, int t_max, void* stream, trs_match_stats* out);
+
 /* ---- SDDMM (no counterpart in the reference; defined by BASELINE config 3) -----------------
  * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e. */
 int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y,

@@ -1,0 +1,79 @@
+"""GPU matching statistics against the reference's own compiled CPU matchers (oracle/_ref) and
+against committed dicts those modules produced (tests/golden/match24.json).  The three CPU
+matchers are deterministic, so the bar is exact equality of every dict entry."""
+import json
+import math
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from trspmm import graphs
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).parent / "golden" / "match24.json"
+
+MODULES = {
+    "para_dr": ("matching_utils", "match_2to4"),
+    "hash": ("matching_utils_hash", "match_2to4_hash"),
+    "bucket": ("matching_utils_bucket", "match_2to4_bucket"),
+}
+
+
+def _graph(spec):
+    kind, kw = spec
+    rp, col, val = getattr(graphs, kind + "_graph")(**kw)
+    return rp.numpy(), col.numpy(), val.numpy()
+
+
+def _same(got, want):
+    assert set(got) == set(want), (sorted(got), sorted(want))
+    for k, v in want.items():
+        if isinstance(v, float):
+            assert math.isclose(got[k], v, rel_tol=1e-12), k
+        else:
+            assert got[k] == v, (k, got[k], v)
+
+
+@pytest.mark.parametrize("variant", sorted(MODULES))
+def test_matches_committed_reference_dicts(variant):
+    import importlib
+    gold = json.loads(GOLD.read_text())
+    mod = importlib.import_module(MODULES[variant][0])
+    fn = getattr(mod, MODULES[variant][1])
+    for case in gold["cases"]:
+        rp, col, val = _graph(case["graph"])
+        for call in case[variant]:
+            _same(fn(rp, col, val, **call["kwargs"]), call["result"])
+
+
+@pytest.mark.parametrize("variant", sorted(MODULES))
+def test_matches_live_reference(variant):
+    import importlib
+    ref = O.reference_module(MODULES[variant][0])
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    mine = getattr(importlib.import_module(MODULES[variant][0]), MODULES[variant][1])
+    theirs = getattr(ref, MODULES[variant][1])
+    specs = [("rmat", dict(scale=13, edge_factor=16, seed=31)), ("clustered", dict(n=8192, community=128, intra=24, glob=4, seed=3)),
+             ("uniform", dict(n=3001, per_row=9, seed=5))]
+    for spec in specs:
+        rp, col, val = _graph(spec)
+        # the reference prints a table from C: silence fd 1 around it
+        saved = os.dup(1); devnull = os.open(os.devnull, os.O_WRONLY); os.dup2(devnull, 1)
+        try:
+            want = dict(theirs(rp, col, val))
+        finally:
+            os.dup2(saved, 1); os.close(saved); os.close(devnull)
+        _same(mine(rp, col, val), want)
+
+
+def test_argument_errors():
+    import matching_utils
+    rp, col, val = _graph(("uniform", dict(n=64, per_row=3, seed=1)))
+    with pytest.raises(RuntimeError):
+        matching_utils.match_2to4(rp, col, val, window_size=0)
+    with pytest.raises(RuntimeError):
+        matching_utils.match_2to4(np.zeros(5, dtype=np.int32), np.zeros(0, dtype=np.int32), np.zeros(0, dtype=np.float32))

@@ -28,6 +28,8 @@ __device__ __forceinline__ float dot8(const uint4& x, const uint4& y) {
     return s;
 }
 
+constexpr int kUnroll = 4;  // entries in flight per 8-lane group
+
 template <bool VEC>
 __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, const int* __restrict__ col,
                                                const __half* __restrict__ X, const __half* __restrict__ Y,
@@ -45,6 +47,38 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
         if ((long long)rowptr[mid] <= e0) lo = mid; else hi = mid;
     }
     int row = lo;
+    if (VEC && K == 64) {
+        // fast path: one 16-byte slice of X[row] and Y[col] per lane; kUnroll independent entries
+        // are loaded before any of them is reduced, so a group keeps kUnroll Y rows in flight
+        int xrow = -1;
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        for (long long eb = e0; eb < e1; eb += 4 * kUnroll) {
+            uint4 yv[kUnroll], xs[kUnroll];
+            bool live[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const long long e = eb + sub + 4 * u;
+                live[u] = e < e1;
+                yv[u] = make_uint4(0, 0, 0, 0);
+                xs[u] = yv[u];
+                if (live[u]) {
+                    while ((long long)rowptr[row + 1] <= e) ++row;
+                    if (row != xrow) { xv = __ldg(reinterpret_cast<const uint4*>(X + (size_t)row * 64) + sl); xrow = row; }
+                    xs[u] = xv;
+                    yv[u] = __ldg(reinterpret_cast<const uint4*>(Y + (size_t)col[e] * 64) + sl);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                float s = dot8(xs[u], yv[u]);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                if (live[u] && sl == 0) out[eb + sub + 4 * u] = __float2half_rn(s);
+            }
+        }
+        return;
+    }
     for (long long eb = e0; eb < e1; eb += 4) {
         const long long e = eb + sub;
         const bool live = e < e1;
