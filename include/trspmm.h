@@ -223,6 +223,7 @@ typedef struct trs_match_stats {
     long long num_16x16_blocks, block_padding_groups, fine_fallback, coarse_fallback, fake_zeros;
     long long tc_total_nnz, tc_block_count; /* variant 0 only */
     int32_t tc_block_max_nnz, tc_block_min_nnz;
+    long long fake_zeros_exact; /* variant 1: 2*rows*groups - nnz, the per-row count block_match_cuda.cu:260-280 makes */
 } trs_match_stats;
 int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, int n_rows, int window,
                       int dense_threshold, int t_max, void* stream, trs_match_stats* out);

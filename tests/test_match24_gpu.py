@@ -77,3 +77,32 @@ def test_argument_errors():
         matching_utils.match_2to4(rp, col, val, window_size=0)
     with pytest.raises(RuntimeError):
         matching_utils.match_2to4(np.zeros(5, dtype=np.int32), np.zeros(0, dtype=np.int32), np.zeros(0, dtype=np.float32))
+
+
+def test_cuda_and_online_entry_points_keep_the_invariants():
+    """matching_utils_cuda / matching_utils_online: the reference versions are race-dependent, so the
+    contract is the set of keys and the invariants its driver checks (test_24_matching.py:170-199,
+    317-344)."""
+    import torch
+    import matching_utils_cuda
+    import matching_utils_online
+    rp, col, val = graphs.rmat_graph(12, 16, seed=8)
+    nnz = col.numel()
+    d = matching_utils_cuda.match_2to4(rp.cuda(), col.cuda(), val.cuda())
+    assert set(d) == {"total_rows", "total_cols", "total_nnz", "sparsity", "num_row_panels", "num_groups",
+                      "num_16x16_blocks", "block_padding_groups", "fine_fallback", "coarse_fallback", "fake_zeros"}
+    assert d["total_nnz"] == nnz and d["num_row_panels"] == 256
+    assert d["block_padding_groups"] == d["num_16x16_blocks"] * 4 - d["num_groups"]
+    assert d["total_nnz"] + d["fake_zeros"] == d["num_groups"] * 32       # every slot is a value or a padded zero
+    assert d == matching_utils_cuda.match_2to4(rp.cuda(), col.cuda(), val.cuda())   # deterministic
+    with pytest.raises(RuntimeError):
+        matching_utils_cuda.match_2to4(rp, col.cuda(), val.cuda())
+    with pytest.raises(RuntimeError):
+        matching_utils_cuda.match_2to4(rp.cuda(), col.cuda(), val.cuda(), window_size=17)
+    o = matching_utils_online.match_2to4_online(rp.numpy(), col.numpy(), val.numpy())
+    assert set(o) == {"total_rows", "total_cols", "total_nnz", "num_sptc_groups", "num_tc_blocks", "dense_to_tc_cols",
+                      "dense_to_sptc_cols", "fine_fb", "coarse_fb_cols", "num_16x16_blocks", "block_padding_groups",
+                      "fake_zeros"}
+    assert o["block_padding_groups"] == o["num_16x16_blocks"] * 4 - o["num_sptc_groups"]
+    assert o["dense_to_tc_cols"] == o["num_tc_blocks"] * 8 and o["dense_to_sptc_cols"] >= 0
+    assert o["total_nnz"] == nnz

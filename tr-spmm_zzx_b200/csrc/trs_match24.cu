@@ -30,6 +30,7 @@ struct MStats {  // device-side accumulators
     long long groups, tc_blocks, blocks16, pad_groups, fine_fb, coarse_fb, fake_zeros;
     long long tc_total_nnz, tc_block_count;
     int tc_max_nnz, tc_min_nnz;
+    long long fake_exact;  // 2 * win_rows * groups - nnz of the grouped columns (exact padding count)
 };
 
 struct WinCols {
@@ -196,7 +197,10 @@ __global__ void km_hash(WinCols wc, Work wk, int W, int n_rows, int window, MSta
     unsigned char *n1 = wk.pn1 + b, *used = wk.pused + b;
     const int* by_mask = wk.idx_a + b;  // local column indices sorted by (mask, index)
     int* top = wk.idx_b + b;            // top[r] for a run starting at sorted position r: next candidate position
-    for (int i = lane; i < n; i += 32) { matched[i] = 0; used[i] = 0; top[i] = -2; }
+    long long win_nnz = 0;
+    for (int i = lane; i < n; i += 32) { matched[i] = 0; used[i] = 0; top[i] = -2; win_nnz += __popc((unsigned)m[i]); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) win_nnz += __shfl_xor_sync(0xffffffffu, win_nnz, o);
     __syncwarp();
     int np = 0, fine = 0, coarse = 0, groups = 0;
     long long fake = 0;
@@ -252,7 +256,10 @@ __global__ void km_hash(WinCols wc, Work wk, int W, int n_rows, int window, MSta
     group_pairs(np, 1024, 1, G1, G2, used, lane,
                 [&](int i, int j) { fake += 2 * win_rows - ((int)n1[i] + n1[j]); ++groups; },
                 [&](int i) { fake += 2 * win_rows - (int)n1[i]; ++groups; coarse += 2; });
-    if (lane == 0) flush_window(st, groups, fake, fine, coarse);
+    if (lane == 0) {
+        flush_window(st, groups, fake, fine, coarse);
+        atomicAdd((u64*)&st->fake_exact, (u64)(2ll * win_rows * groups - win_nnz));
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -591,5 +598,6 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
     out->tc_block_count = h.tc_block_count;
     out->tc_block_max_nnz = h.tc_max_nnz;
     out->tc_block_min_nnz = h.tc_min_nnz;
+    out->fake_zeros_exact = h.fake_exact;
     return TRS_OK;
 }

@@ -19,7 +19,8 @@ class TrsMatchStats(C.Structure):
                 ("num_tc_blocks", C.c_longlong), ("num_16x16_blocks", C.c_longlong),
                 ("block_padding_groups", C.c_longlong), ("fine_fallback", C.c_longlong),
                 ("coarse_fallback", C.c_longlong), ("fake_zeros", C.c_longlong), ("tc_total_nnz", C.c_longlong),
-                ("tc_block_count", C.c_longlong), ("tc_block_max_nnz", C.c_int32), ("tc_block_min_nnz", C.c_int32)]
+                ("tc_block_count", C.c_longlong), ("tc_block_max_nnz", C.c_int32), ("tc_block_min_nnz", C.c_int32),
+                ("fake_zeros_exact", C.c_longlong)]
 
 
 def _as_int32(x: int) -> int:
