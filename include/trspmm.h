@@ -118,7 +118,7 @@ int trs_spmm_status(const trs_spmm_plan* plan, int* status);
  * windows in a fixed array inside the library (TRS_STATIC_SCRATCH_BYTES per GPU, held from
  * library load to process exit) and allocates nothing, on the host or the device.
  *   - returns TRS_E_LIMIT when the plan needs more scratch for this F than the array holds
- *     (trs_spmm_workspace_bytes tells the need); nothing is launched then;
+ *     (trs_spmm_static_scratch_bytes tells the need); nothing is launched then;
  *   - the first call on each device looks up the array's device address; make that call before
  *     any stream capture starts on that device;
  *   - all calls on a device share the one array: calls whose kernels may overlap on the GPU
@@ -127,6 +127,7 @@ int trs_spmm_status(const trs_spmm_plan* plan, int* status);
 #define TRS_STATIC_SCRATCH_BYTES (8u << 20)
 int trs_spmm_run_static(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
                         void* stream);
+int trs_spmm_static_scratch_bytes(const trs_spmm_plan* plan, int F, size_t* bytes);
 /* Number of kernels one trs_spmm_run launches (1, or 2 when some window is split). */
 int trs_spmm_launches(const trs_spmm_plan* plan);
 

@@ -32,7 +32,7 @@ def _plan(monkeypatch, scale, chunk):
 def test_static_scratch_entry_matches_ordinary_entry(monkeypatch):
     plan, n = _plan(monkeypatch, 11, 16)
     F = 128
-    need = plan.workspace_bytes(F)
+    need = plan.static_scratch_bytes(F)
     assert 0 < need <= 8 << 20, "the case must use scratch and fit the fixed array"
     g = torch.Generator().manual_seed(5)
     for call in range(2):  # two calls in a row share the array; the second must not see the first
@@ -50,7 +50,7 @@ def test_static_scratch_entry_matches_ordinary_entry(monkeypatch):
 def test_static_scratch_entry_refuses_oversized_plans(monkeypatch):
     plan, n = _plan(monkeypatch, 13, 8)
     F = 256
-    assert plan.workspace_bytes(F) > 8 << 20
+    assert plan.static_scratch_bytes(F) > 8 << 20
     B = torch.randn(n, F).half().cuda()
     out = torch.full((n, F), 3.0, device="cuda")
     with pytest.raises(TrsError) as e:

@@ -19,6 +19,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 #include "trs_common.cuh"
 
@@ -717,6 +718,277 @@ __global__ void k_expand_tc(const long long* __restrict__ t_binary, const int* _
     dense[i] = v;
 }
 
+// ----------------------------------------------------------------------------------------------
+// Persistent "flat stream" variant.  All k-steps of the matrix form one list ordered by window
+// (a window's packed tiles, then its TC block pairs); the plan cuts the list into one contiguous
+// chunk per resident CTA, balanced by steps plus a fixed cost per window.  A CTA streams through
+// its chunk with the gather pipeline never draining: when a window ends it writes the 16 rows
+// while the loads of the next windows are already in flight.  This removes the per-window
+// pipeline fill / drain of the item-per-CTA kernels, which dominates for windows of a few dozen
+// steps.  Per step the kernel reads an 8-byte descriptor (tile or TC-pair index, window id,
+// first/last-of-window flags) that runs kMetaAhead steps ahead of the compute; column ids run
+// kIdxAhead ahead and B rows kStages-1 ahead, all through cp.async groups.
+// Windows cut by a chunk boundary write fp32 partial sums to two fixed scratch slots per CTA;
+// k_reduce_flat adds them in chunk order (deterministic).
+// ----------------------------------------------------------------------------------------------
+constexpr int kMetaAhead = 10;
+constexpr int kMetaRing = 16;
+constexpr unsigned kDescLast = 0x80000000u, kDescFirst = 0x40000000u, kDescTc = 0x20000000u,
+                   kDescTcSecond = 0x10000000u, kDescIndex = 0x0FFFFFFFu;
+
+struct FlatArgs {
+    const int2* meta;         // [S] {descriptor, window}
+    const int* chunk_begin;   // [G + 1]
+    int G;
+};
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_flat(const KernelArgs a, const FlatArgs fa) {
+    using T = Tile<WARPS>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int fbase = blockIdx.y * T::FS;
+    const int chunk = blockIdx.x;
+    const int g0 = fa.chunk_begin[chunk];
+    const int nsteps = fa.chunk_begin[chunk + 1] - g0;
+    if (nsteps <= 0) return;
+
+    const uint32_t smem0 = smem_u32(smem);
+    constexpr int RING_OFF = T::STAGE * kStages;            // ids ring: kIdxRing x 64 B
+    constexpr int META_OFF = RING_OFF + kIdxRing * 64;      // meta ring: kMetaRing x 8 B
+    const int* ring = (const int*)(smem + RING_OFF);
+    const int2* mring = (const int2*)(smem + META_OFF);
+
+    const int ch = tid % T::CPR, row0 = tid / T::CPR;
+    const uint32_t pitch16 = (uint32_t)a.F >> 3;
+    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;
+    const bool fin = fbase + ch * 8 < a.F;
+    const uint4* Bq = (const uint4*)a.B;
+    const uint32_t dst0 = smem0 + row0 * T::ROWB + ch * 16;
+    const int mtx = lane >> 3;
+    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + (wid * 32 + (mtx >> 1) * 8) * 2;
+    const unsigned char* a_lane = smem + T::BBYTES;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    auto issue_meta = [&](int m) {
+        if (tid == 0 && m < nsteps)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem0 + META_OFF + (m & (kMetaRing - 1)) * 8),
+                         "l"(fa.meta + (size_t)(g0 + m)));
+    };
+    auto issue_idx = [&](int m) {
+        if (tid < 4 && m < nsteps) {
+            const unsigned desc = (unsigned)mring[m & (kMetaRing - 1)].x;
+            const unsigned index = desc & kDescIndex;
+            const uint32_t dst = smem0 + RING_OFF + (m & (kIdxRing - 1)) * 64 + tid * 16;
+            if (!(desc & kDescTc)) {
+                cp_async16(dst, a.f.s_tile_column + (size_t)index * 16 + tid * 4, 16);
+            } else if (tid < 2 || (desc & kDescTcSecond)) {
+                cp_async16(dst, a.f.t_column + (size_t)(index + (tid >> 1)) * 8 + (tid & 1) * 4, 16);
+            } else {
+                *(int4*)(smem + RING_OFF + (m & (kIdxRing - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
+            }
+        }
+    };
+    auto issue = [&](int j, int stage) {
+        const int* cols = ring + (j & (kIdxRing - 1)) * 16;
+        const int c0 = cols[row0], c1 = cols[row0 + 8];
+        const uint32_t o0 = (uint32_t)max(c0, 0) * pitch16 + chunk16;
+        const uint32_t o1 = (uint32_t)max(c1, 0) * pitch16 + chunk16;
+        cp_async16(dst0 + stage * T::STAGE, Bq + o0, (c0 >= 0 && fin) ? 16 : 0);
+        cp_async16(dst0 + stage * T::STAGE + 8 * T::ROWB, Bq + o1, (c1 >= 0 && fin) ? 16 : 0);
+        if (tid < 32) {
+            const unsigned desc = (unsigned)mring[j & (kMetaRing - 1)].x;
+            const size_t index = desc & kDescIndex;
+            const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + tid * 16;
+            if (!(desc & kDescTc)) {
+                if (tid < 16) cp_async16(adst, a.f.s_packed_a + index * 64 + tid * 4, 16);
+                else if (tid < 18) cp_async16(adst, a.f.s_packed_meta + index * 8 + (tid - 16) * 4, 16);
+            } else {
+                const bool live = tid < 16 || (desc & kDescTcSecond);
+                cp_async16(adst, a.tc_dense + (index + (live ? (tid >> 4) : 0)) * 128 + (tid & 15) * 8, live ? 16 : 0);
+            }
+        }
+    };
+    auto compute = [&](bool dense, int stage) {
+        const unsigned char* as = a_lane + stage * T::STAGE;
+        const uint32_t baddr = boff + stage * T::STAGE;
+        if (!dense) {
+            const uint2 av = *(const uint2*)(as + lane * 8);
+            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+            }
+        } else {
+            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
+            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
+            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
+            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+    };
+
+    // ---- prologue: three dependent fills, paid once per chunk -------------------------------------
+#pragma unroll
+    for (int m = 0; m < kMetaAhead; ++m) issue_meta(m);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < kIdxAhead; ++m) issue_idx(m);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kStages - 1; ++j) {
+        if (j < nsteps) issue(j, j);
+        cp_async_commit();
+    }
+    bool piece_first = true;  // does the current piece contain its window's first step?  (set below)
+    bool piece_open = false;
+    for (int j0 = 0; j0 < nsteps; j0 += kStages) {
+#pragma unroll
+        for (int u = 0; u < kStages; ++u) {
+            const int j = j0 + u;
+            if (j < nsteps) {
+                cp_async_wait<kStages - 2>();
+                __syncthreads();
+                issue_meta(j + kMetaAhead);
+                issue_idx(j + kIdxAhead);
+                if (j + kStages - 1 < nsteps) issue(j + kStages - 1, (u + kStages - 1) % kStages);
+                cp_async_commit();
+                const int2 mt = mring[j & (kMetaRing - 1)];
+                const unsigned desc = (unsigned)mt.x;
+                if (!piece_open) { piece_open = true; piece_first = (desc & kDescFirst) != 0; }
+                compute((desc & kDescTc) != 0, u);
+                if ((desc & kDescLast) || j == nsteps - 1) {
+                    // the piece ends here: whole window -> C; otherwise a partial-sum slot
+                    const bool whole = piece_first && (desc & kDescLast);
+                    Item it;
+                    it.window = mt.y;
+                    it.step_begin = piece_first ? 0 : 1;  // only the piece with the first step adds the CSR parts
+                    it.step_end = 0;
+                    it.slot = whole ? -1 : (piece_first ? 2 * chunk + 1 : 2 * chunk);
+                    it.tile0 = it.ntiles = it.blk0 = it.blk_end = 0;
+                    finish_item(acc, it, a, fbase, wid, g, t);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) acc[i][k] = 0.f;
+                    piece_open = false;
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+// Windows without any k-step (empty, or CSR parts only): zeros plus the CSR parts.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) k_window_nosteps(const KernelArgs a, const int* __restrict__ windows) {
+    using T = Tile<WARPS>;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    Item it;
+    it.window = windows[blockIdx.x];
+    it.step_begin = 0; it.step_end = 0; it.slot = -1;
+    it.tile0 = it.ntiles = it.blk0 = it.blk_end = 0;
+    finish_item(acc, it, a, blockIdx.y * T::FS, wid, lane >> 2, lane & 3);
+}
+
+// One block per chunk boundary: if the boundary cuts a window and is the first cut of that window,
+// add the window's pieces in chunk order and write its rows.
+__global__ void k_reduce_flat(const FlatArgs fa, const float* __restrict__ scratch, void* C, int F, int m_rows, int window,
+                              int out_half, int relu) {
+    const int c = blockIdx.x + 1;  // boundary between chunk c-1 and chunk c
+    const int b = fa.chunk_begin[c];
+    if (b <= fa.chunk_begin[c - 1] && c > 1) {
+        // empty chunk c-1: the cut (if any) belongs to an earlier boundary with the same position
+        if (fa.chunk_begin[c - 1] == b) return;
+    }
+    if (b >= fa.chunk_begin[fa.G]) return;
+    const int2 here = fa.meta[b];
+    if ((unsigned)here.x & kDescFirst) return;  // the boundary falls between two windows
+    const int w = here.y;
+    // first cut of this window?  the chunk before must hold the window's first step
+    int cp = c - 1;
+    while (cp > 0 && fa.chunk_begin[cp] == b) --cp;  // skip empty chunks at the same position
+    const int pb = fa.chunk_begin[cp];
+    if (fa.meta[pb].y == w && !((unsigned)fa.meta[pb].x & kDescFirst)) return;  // the window was already cut earlier
+    const int per = 16 * F;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int lr = i / F, f = i % F;
+        const long long row = (long long)w * window + lr;
+        if (lr >= window || row >= m_rows) continue;
+        float s = scratch[(size_t)(2 * cp + 1) * per + i];  // tail piece of the chunk with the first step
+        for (int cc = c; cc < fa.G; ++cc) {
+            const int bb = fa.chunk_begin[cc];
+            if (bb >= fa.chunk_begin[cc + 1]) continue;  // empty chunk
+            const int2 m2 = fa.meta[bb];
+            if (m2.y != w || ((unsigned)m2.x & kDescFirst)) break;
+            s += scratch[(size_t)(2 * cc) * per + i];       // head piece of a later chunk
+        }
+        if (relu) s = fmaxf(s, 0.f);
+        if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
+        else ((float*)C)[(size_t)row * F + f] = s;
+    }
+}
+
+// step descriptors: one thread per step
+__global__ void k_fill_meta(trs_format f, WindowRanges wr, const int* __restrict__ win_step_off, int W, int S,
+                            int2* __restrict__ meta) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= S) return;
+    int lo = 0, hi = W;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (win_step_off[mid] <= s) lo = mid; else hi = mid; }
+    const int w = lo;
+    const int first = win_step_off[w], last = win_step_off[w + 1] - 1;
+    const int tile0 = w < f.num_windows ? f.s_window_tile_offset[w] : 0;
+    const int ntiles = w < f.num_windows ? f.s_window_tile_offset[w + 1] - tile0 : 0;
+    const int local = s - first;
+    unsigned desc;
+    if (local < ntiles) desc = (unsigned)(tile0 + local);
+    else {
+        const int blk = wr.blk_begin[w] + 2 * (local - ntiles);
+        desc = kDescTc | (unsigned)blk | (blk + 1 < wr.blk_end[w] ? kDescTcSecond : 0u);
+    }
+    if (s == first) desc |= kDescFirst;
+    if (s == last) desc |= kDescLast;
+    meta[s] = make_int2((int)desc, w);
+}
+
+__global__ void k_window_steps(trs_format f, WindowRanges wr, int W, int* __restrict__ steps) {
+    const int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w > W) return;
+    int n = 0;
+    if (w < W) {
+        if (w < f.num_windows) n = f.s_window_tile_offset[w + 1] - f.s_window_tile_offset[w];
+        n += (wr.blk_end[w] - wr.blk_begin[w] + 1) / 2;
+    }
+    steps[w] = n;
+}
+
 // Adds the partial sums of a split window in slot order and writes its 16 rows of C.
 __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __restrict__ scratch, void* C, int F,
                                int m_rows, int window, int out_half, int relu) {
@@ -753,6 +1025,11 @@ struct trs_spmm_plan {
     int n_items, n_heavy, n_slots;
     bool bulk_ok;                     // bulk-copy kernel requested and usable
     bool arrays_aligned;              // index / tile arrays are 16-byte aligned
+    // persistent flat-stream kernel
+    bool flat_ok = false;
+    int flat_G = 0, flat_S = 0, n_nosteps = 0;
+    DevBuf<int2> step_meta;
+    DevBuf<int> chunk_begin, nosteps;
 };
 
 static int env_int(const char* name, int dflt) {
@@ -808,6 +1085,79 @@ static int validate_on_device(const trs_format& f, int m_rows, int k_cols, int w
     if (h_err & V_COLUMN) return TRS_E_COLUMN;
     if (h_err & V_ROW) return TRS_E_ROW;
     return TRS_OK;
+}
+
+// Flat-stream structures: steps per window -> prefix -> per-step descriptors; the step list is cut
+// into one chunk per resident CTA, balanced by steps + a fixed cost per window end.
+static int build_flat(trs_spmm_plan* p, cudaStream_t st) {
+    const int W = p->num_windows;
+    DevBuf<int> steps, off;
+    DevBuf<unsigned char> tmp;
+    int rc = steps.alloc((size_t)W + 1);
+    if (!rc) rc = off.alloc((size_t)W + 1);
+    auto done = [&](int code) { steps.release(); off.release(); tmp.release(); return code; };
+    if (rc) return done(rc);
+    k_window_steps<<<(unsigned)((W + 1 + 255) / 256), 256, 0, st>>>(p->f, p->wr, W, steps.p);
+    size_t tb = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, tb, steps.p, off.p, W + 1, st);
+    rc = tmp.alloc(tb + 16);
+    if (rc) return done(rc);
+    cub::DeviceScan::ExclusiveSum(tmp.p, tb, steps.p, off.p, W + 1, st);
+    std::vector<int> h_off((size_t)W + 1);
+    cudaError_t e = cudaMemcpyAsync(h_off.data(), off.p, sizeof(int) * ((size_t)W + 1), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return done((int)e);
+    const int S = h_off[W];
+    p->flat_S = S;
+    // windows without steps get their own tiny kernel
+    std::vector<int> nos;
+    for (int w = 0; w < W; ++w)
+        if (h_off[w + 1] == h_off[w]) nos.push_back(w);
+    p->n_nosteps = (int)nos.size();
+    rc = p->nosteps.alloc(nos.size());
+    if (rc) return done(rc);
+    if (!nos.empty()) cudaMemcpyAsync(p->nosteps.p, nos.data(), sizeof(int) * nos.size(), cudaMemcpyHostToDevice, st);
+    // chunk boundaries
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // one chunk per CTA that can be resident at once (the F = 128 kernel is the largest one)
+    int occ = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_window_spmm_flat<4>, 128, Tile<4>::SMEM + kMetaRing * 8);
+    const int per_sm = max(1, env_int("TRS_FLAT_CTAS_PER_SM", occ > 0 ? occ : 8));
+    int G = sms * per_sm;
+    if (S < G * 8) G = max(1, S / 8);
+    const double win_cost = (double)env_int("TRS_FLAT_WINDOW_COST", 4);
+    std::vector<int> cb((size_t)G + 1, S);
+    cb[0] = 0;
+    if (S > 0) {
+        // cost position of step s inside window w: s + win_cost * (non-empty windows finished before w)
+        const double total = (double)S + win_cost * (double)(W - (int)nos.size());
+        int w = 0;
+        double done_windows = 0;  // non-empty windows fully before w
+        for (int c = 1; c < G; ++c) {
+            const double target = total * c / G;
+            while (w < W && (double)h_off[w + 1] + win_cost * (done_windows + (h_off[w + 1] > h_off[w] ? 1 : 0)) <= target) {
+                if (h_off[w + 1] > h_off[w]) done_windows += 1;
+                ++w;
+            }
+            int s = w < W ? (int)(target - win_cost * done_windows) : S;
+            if (w < W) s = min(max(s, h_off[w]), h_off[w + 1]);
+            cb[c] = max(cb[c - 1], min(s, S));
+        }
+    }
+    p->flat_G = G;
+    rc = p->chunk_begin.alloc((size_t)G + 1);
+    if (!rc) rc = p->step_meta.alloc((size_t)max(S, 1));
+    if (rc) return done(rc);
+    cudaMemcpyAsync(p->chunk_begin.p, cb.data(), sizeof(int) * ((size_t)G + 1), cudaMemcpyHostToDevice, st);
+    if (S > 0)
+        k_fill_meta<<<(unsigned)((S + 255) / 256), 256, 0, st>>>(p->f, p->wr, off.p, W, S, p->step_meta.p);
+    e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return done((int)e);
+    p->flat_ok = true;
+    return done(0);
 }
 
 // CSR value-count checks need the last prefix entry; done with the column range check so that a
@@ -902,6 +1252,14 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     const char* kv = getenv("TRS_SPMM_KERNEL");
     p->arrays_aligned = (align_or & 15) == 0;
     p->bulk_ok = p->arrays_aligned && kv && strcmp(kv, "bulk") == 0;
+    // The persistent flat-stream schedule is opt-in (TRS_SPMM_KERNEL=flat).  Measured on B200 it is
+    // slower than one CTA per window (4.95 vs 3.23 ms at R-MAT scale 21): the gather is bound by how
+    // many bytes the SM keeps in flight, the flat kernel fits 8 CTAs per SM instead of 10, and the
+    // pipeline bubbles it removes were not the limiter.
+    if (p->arrays_aligned && kv && strcmp(kv, "flat") == 0) {
+        rc = build_flat(p, st);
+        if (rc) { trs_spmm_plan_destroy(p); return rc; }
+    }
     *out_plan = p;
     return TRS_OK;
 }
@@ -920,17 +1278,59 @@ extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
     p->heavy.release();
     p->tc_dense.release();
     p->zeros.release();
+    p->step_meta.release();
+    p->chunk_begin.release();
+    p->nosteps.release();
     delete p;
     return TRS_OK;
 }
 
+static size_t items_scratch_bytes(const trs_spmm_plan* p, int F) { return (size_t)p->n_slots * 16 * (size_t)F * sizeof(float); }
+static size_t flat_scratch_bytes(const trs_spmm_plan* p, int F) {
+    return p->flat_ok ? (size_t)2 * p->flat_G * 16 * (size_t)F * sizeof(float) : 0;
+}
+static bool flat_usable(const trs_spmm_plan* p, int F) { return p->flat_ok && p->flat_S > 0 && F % 8 == 0; }
+
 extern "C" int trs_spmm_workspace_bytes(const trs_spmm_plan* p, int F, size_t* bytes) {
     if (!p || !bytes || F <= 0) return TRS_E_ARG;
-    *bytes = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
+    // the flat-stream kernel needs two slots per chunk; an unaligned B falls back to the item
+    // kernels, so report what either path may ask for
+    const size_t a = items_scratch_bytes(p, F), b = flat_usable(p, F) ? flat_scratch_bytes(p, F) : 0;
+    *bytes = a > b ? a : b;
     return TRS_OK;
 }
 
-extern "C" int trs_spmm_launches(const trs_spmm_plan* p) { return p ? (p->n_heavy > 0 ? 2 : 1) : 0; }
+extern "C" int trs_spmm_static_scratch_bytes(const trs_spmm_plan* p, int F, size_t* bytes) {
+    if (!p || !bytes || F <= 0) return TRS_E_ARG;
+    *bytes = items_scratch_bytes(p, F);
+    return TRS_OK;
+}
+
+extern "C" int trs_spmm_launches(const trs_spmm_plan* p) {
+    if (!p) return 0;
+    if (p->flat_ok && p->flat_S > 0) return 1 + (p->flat_G > 1 ? 1 : 0) + (p->n_nosteps > 0 ? 1 : 0);
+    return p->n_heavy > 0 ? 2 : 1;
+}
+
+template <int WARPS>
+static int launch_flat_kernel(const trs_spmm_plan* p, const KernelArgs& a, cudaStream_t st) {
+    using T = Tile<WARPS>;
+    constexpr int SMEM = T::SMEM + kMetaRing * 8;
+    FlatArgs fa{p->step_meta.p, p->chunk_begin.p, p->flat_G};
+    const int slabs = ceil_div(a.F, T::FS);
+    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_flat<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    k_window_spmm_flat<WARPS><<<dim3(p->flat_G, slabs), T::THREADS, SMEM, st>>>(a, fa);
+    TRS_LAUNCH_CHECK();
+    if (p->n_nosteps > 0) {
+        k_window_nosteps<WARPS><<<dim3(p->n_nosteps, slabs), T::THREADS, 0, st>>>(a, p->nosteps.p);
+        TRS_LAUNCH_CHECK();
+    }
+    if (p->flat_G > 1) {
+        k_reduce_flat<<<p->flat_G - 1, 256, 0, st>>>(fa, a.scratch, a.C, a.F, a.m_rows, a.window, a.out_half, a.relu);
+        TRS_LAUNCH_CHECK();
+    }
+    return TRS_OK;
+}
 
 template <int WARPS>
 static int launch_bulk_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
@@ -967,12 +1367,22 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
     return trs_spmm_run_ex(p, B, C, F, out_dtype, 0, workspace, workspace_bytes, stream);
 }
 
+static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
+                    size_t workspace_bytes, void* stream, bool items_only);
+
 extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
                                void* workspace, size_t workspace_bytes, void* stream) {
+    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, false);
+}
+
+static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
+                    size_t workspace_bytes, void* stream, bool items_only) {
     if (!p || !B || !C || F <= 0) return TRS_E_ARG;
     if (flags & ~TRS_EPILOGUE_RELU) return TRS_E_ARG;
     if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
-    size_t need = (size_t)p->n_slots * 16 * (size_t)F * sizeof(float);
+    const bool flat = !items_only && flat_usable(p, F) && (((uintptr_t)B & 15) == 0);
+    size_t need = flat ? flat_scratch_bytes(p, F) : items_scratch_bytes(p, F);
+    if (flat && p->flat_G <= 1) need = 0;
     if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     KernelArgs a;
@@ -982,6 +1392,11 @@ extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* 
     a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
     a.tc_dense = p->tc_dense.p; a.zeros = p->zeros.p; a.status = (int*)(p->zeros.p + 512);
     int rc;
+    if (flat) {
+        if (F <= 32) return launch_flat_kernel<1>(p, a, st);
+        if (F <= 64) return launch_flat_kernel<2>(p, a, st);
+        return launch_flat_kernel<4>(p, a, st);
+    }
     const bool bulk = p->bulk_ok && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
     if (bulk) {
         if (F <= 32) rc = launch_bulk_kernel<1>(a, p->n_items, st);
@@ -1004,8 +1419,9 @@ extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* 
 // Some hosts cannot give this library scratch memory at call time: applications that hand the
 // whole device memory to their own pool at start-up (a later cudaMalloc from a plug-in fails or
 // fragments that pool) and latency-critical loops in which cudaMalloc / cudaFree would stall
-// every stream of the device.  For them trs_spmm_run_static runs the same kernels as
-// trs_spmm_run, with the partial sums of split windows kept in the array below instead of a
+// every stream of the device.  For them trs_spmm_run_static runs the window-per-CTA kernels
+// (k_window_spmm_lean / k_window_spmm + k_reduce_heavy), whose scratch need is small and known
+// from the plan, with the partial sums of split windows kept in the array below instead of a
 // caller-provided workspace.  Every GPU that loads the library holds these bytes until exit.
 //
 // In host code the array's name is only a stand-in for the symbol; the device address is asked
@@ -1040,5 +1456,5 @@ extern "C" int trs_spmm_run_static(const trs_spmm_plan* p, const trs_half* B, vo
     }
     // Nothing in the array has to start at zero: every slot a call reads is first written in
     // full by that call's window kernel.
-    return trs_spmm_run(p, B, C, F, out_dtype, scratch, (size_t)TRS_STATIC_SCRATCH_BYTES, stream);
+    return run_impl(p, B, C, F, out_dtype, 0, scratch, (size_t)TRS_STATIC_SCRATCH_BYTES, stream, /*items_only=*/true);
 }

@@ -78,6 +78,8 @@ def load():
     lib.trs_spmm_run_ex.restype = i32
     lib.trs_spmm_run_static.argtypes = [vp, vp, vp, i32, i32, vp]
     lib.trs_spmm_run_static.restype = i32
+    lib.trs_spmm_static_scratch_bytes.argtypes = [vp, i32, C.POINTER(sz)]
+    lib.trs_spmm_static_scratch_bytes.restype = i32
     lib.trs_spmm_forward_host.argtypes = [C.POINTER(TrsFormat), vp, vp, i32, i32, i32, i32, i32, C.POINTER(TrsTiming)]
     lib.trs_resident_create.argtypes = [C.POINTER(TrsFormat), i32, i32, i32, i32, C.POINTER(vp)]
     lib.trs_resident_create_device.argtypes = [C.POINTER(TrsFormat), i32, i32, i32, i32, C.POINTER(vp)]

@@ -45,6 +45,12 @@ class SpmmPlan:
         _lib.check(self.lib.trs_spmm_workspace_bytes(self._handle, int(F), C.byref(n)))
         return n.value
 
+    def static_scratch_bytes(self, F: int) -> int:
+        """Bytes of the library's fixed scratch array run_static would use for feature width F."""
+        n = C.c_size_t()
+        _lib.check(self.lib.trs_spmm_static_scratch_bytes(self._handle, int(F), C.byref(n)))
+        return n.value
+
     def status(self) -> int:
         """0, or non-zero when a bounded wait inside a kernel gave up (synchronises the device)."""
         v = C.c_int()
