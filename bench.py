@@ -327,6 +327,98 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_sddmm(args):
+    """SDDMM (BASELINE config 3): X, Y dense N x 64 fp16 on the pattern of the chosen workload."""
+    from trspmm import sddmm
+    dev = torch.device("cuda", 0)
+    rp, col, val, _ = make_matrix(args.workload, dev)
+    n, nnz, K = rp.numel() - 1, col.numel(), 64
+    g = torch.Generator(device=dev).manual_seed(1)
+    X = torch.randn(n, K, device=dev, generator=g).half()
+    Y = torch.randn(n, K, device=dev, generator=g).half()
+    out = sddmm(rp, col, X, Y)
+    for _ in range(args.warmup):
+        sddmm(rp, col, X, Y, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            sddmm(rp, col, X, Y, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, src = peaks()
+    alg = nnz * 4 + (n + 1) * 4 + 2 * n * K * 2 + nnz * 2
+    line = {"metric": "SDDMM GFLOP/s (2*nnz*K)", "value": 2.0 * nnz * K / (ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "f16 in / f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "op": "sddmm", "n_rows": n, "nnz": nnz, "K": K},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None, "kernel": "k_sddmm"},
+            "gpu_launches": args.steps, "clocks": clocks.summary()}
+    if not args.no_cpu:
+        from oracle import oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        rpc, colc, Xc, Yc = rp.cpu(), col.cpu(), X.cpu(), Y.cpu()
+        sample = min(nnz, 4_000_000)   # bounded sample: the first rows holding ~4 M entries
+        rows = int(torch.searchsorted(rpc.long(), torch.tensor(sample))) or 1
+        t0 = time.perf_counter()
+        O.sddmm_csr(rpc[:rows + 1], colc[:int(rpc[rows])], Xc[:rows], Yc)
+        sec = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 2.0 * int(rpc[rows]) * K / sec / 1e9, "unit": "GFLOP/s", "cores": os.cpu_count(),
+                                "kind": "port", "sample": f"first {rows} rows ({int(rpc[rows])} entries), gathered fp32 dot products"}
+    print(json.dumps(line), flush=True)
+
+
+def run_gcn(args, rank, world, local_rank):
+    """Two-layer GCN forward (BASELINE config 4 shape): features 256 -> 128 -> 64, ReLU between."""
+    import torch.distributed as dist
+    from trspmm import ShardedGCN2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rp, col, val, _ = make_matrix(args.workload, dev)
+    n, nnz = rp.numel() - 1, col.numel()
+    g = torch.Generator(device=dev).manual_seed(1)
+    X = torch.randn(n, 256, device=dev, generator=g).half()
+    W1 = (torch.randn(256, 128, device=dev, generator=g) * 0.02).half()
+    W2 = (torch.randn(128, 64, device=dev, generator=g) * 0.02).half()
+    model = ShardedGCN2(rp, col, val, rank, world)
+    kept = model.stats["nnz"] - model.stats["dropped_nnz"]
+    for _ in range(args.warmup):
+        model.forward(X, W1, W2, gather=args.gather)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        model.forward(X, W1, W2, gather=args.gather)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps, float(kept)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        ms = t[0:1].clone(); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        k = t[1:2].clone(); dist.all_reduce(k, op=dist.ReduceOp.SUM)
+        t = torch.cat([ms, k])
+    if rank == 0:
+        ms, kept_total = float(t[0]), float(t[1])
+        flops = 2.0 * kept_total * (128 + 64) + 2.0 * n * (256 * 128 + 128 * 64)
+        print(json.dumps({"metric": "GCN 2-layer forward GFLOP/s (SpMM 2*nnz*(128+64) + dense GEMMs, counted once)",
+                          "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                          "dtype": "f16 in / f32 accumulate", "data": "synthetic",
+                          "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather,
+                                     "n_rows": n, "nnz": nnz, "kept_nnz": int(kept_total),
+                                     "gather_bytes_received_rank0": model.gather_bytes}}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -335,6 +427,9 @@ def main():
     ap.add_argument("--workload", default="rmat21", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn"],
+                    help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
+    ap.add_argument("--gather", default="h1", choices=["h1", "z2"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -342,6 +437,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.op == "sddmm":
+        if rank == 0:
+            run_sddmm(args)
+    elif args.op == "gcn":
+        run_gcn(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -12,7 +12,7 @@
 
 namespace trs {
 
-constexpr int kEntriesPerWarp = 256;
+constexpr int kEntriesPerWarp = 512;
 
 __device__ __forceinline__ float dot8(const uint4& x, const uint4& y) {
     const __half2* xh = reinterpret_cast<const __half2*>(&x);
@@ -28,7 +28,7 @@ __device__ __forceinline__ float dot8(const uint4& x, const uint4& y) {
     return s;
 }
 
-constexpr int kUnroll = 4;  // entries in flight per 8-lane group
+constexpr int kUnroll = 8;  // entries in flight per 8-lane group
 
 template <bool VEC>
 __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, const int* __restrict__ col,
@@ -48,33 +48,36 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
     }
     int row = lo;
     if (VEC && K == 64) {
-        // fast path: one 16-byte slice of X[row] and Y[col] per lane; kUnroll independent entries
-        // are loaded before any of them is reduced, so a group keeps kUnroll Y rows in flight
+        // fast path: one 16-byte slice of X[row] and Y[col] per lane.  The Y slices of kUnroll
+        // entries are requested before any is consumed, so an 8-lane group keeps kUnroll random
+        // 128-byte rows in flight; X[row] changes rarely and is (re)read at use (an L1 hit).
         int xrow = -1;
         uint4 xv = make_uint4(0, 0, 0, 0);
         for (long long eb = e0; eb < e1; eb += 4 * kUnroll) {
-            uint4 yv[kUnroll], xs[kUnroll];
-            bool live[kUnroll];
+            uint4 yv[kUnroll];
+            int rows[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 const long long e = eb + sub + 4 * u;
-                live[u] = e < e1;
+                rows[u] = -1;
                 yv[u] = make_uint4(0, 0, 0, 0);
-                xs[u] = yv[u];
-                if (live[u]) {
+                if (e < e1) {
                     while ((long long)rowptr[row + 1] <= e) ++row;
-                    if (row != xrow) { xv = __ldg(reinterpret_cast<const uint4*>(X + (size_t)row * 64) + sl); xrow = row; }
-                    xs[u] = xv;
+                    rows[u] = row;
                     yv[u] = __ldg(reinterpret_cast<const uint4*>(Y + (size_t)col[e] * 64) + sl);
                 }
             }
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
-                float s = dot8(xs[u], yv[u]);
+                if (rows[u] >= 0 && rows[u] != xrow) {
+                    xrow = rows[u];
+                    xv = __ldg(reinterpret_cast<const uint4*>(X + (size_t)xrow * 64) + sl);
+                }
+                float s = dot8(xv, yv[u]);
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if (live[u] && sl == 0) out[eb + sub + 4 * u] = __float2half_rn(s);
+                if (rows[u] >= 0 && sl == 0) out[eb + sub + 4 * u] = __float2half_rn(s);
             }
         }
         return;

@@ -12,3 +12,4 @@ from .sddmm import sddmm  # noqa: F401
 from .builder import build_format  # noqa: F401
 from .gcn import ShardedGCN2  # noqa: F401
 from . import shard  # noqa: F401
+from .dataset import GCN_dataset_tcu_sptc_cuda_online, edges_to_csr, kernel_tcu_sptc_cuda_online  # noqa: F401
