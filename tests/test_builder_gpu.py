@@ -139,3 +139,23 @@ def test_built_format_feeds_spmm():
     assert plan.status() == 0
     ref = O.spmm_from_format([a.cpu() for a in fmt.arrays()], B, n)
     assert O.scaled_max_error(out, ref) <= 2e-5
+
+
+def test_builder_many_heavy_windows():
+    """Several windows above the block-cooperative threshold (> 4096 units each) with different tie
+    structures, next to light windows: the cooperative partition path must reproduce std::sort's
+    order exactly like the single-thread path does."""
+    g = torch.Generator().manual_seed(5)
+    n = 40000
+    rows, cols = [], []
+    for win, (deg, lo) in enumerate([(3000, 0), (1200, 5000), (700, 100), (5000, 20000)]):
+        for r in range(16):
+            k = deg if r % 3 else deg // 2
+            rows.append(torch.full((k,), win * 64 + r))
+            cols.append(torch.randint(lo, n, (k,), generator=g))
+    rows.append(torch.randint(0, n, (3 * n,), generator=g)); cols.append(torch.randint(0, n, (3 * n,), generator=g))
+    rp, col, _ = graphs.coo_to_csr(torch.cat(rows), torch.cat(cols), n, n)
+    val = torch.randn(col.numel(), generator=g)
+    want, _ = O.build_format(rp, col, val)
+    fmt, _ = build_format(rp.cuda(), col.cuda(), val.cuda())
+    _same(fmt, want)

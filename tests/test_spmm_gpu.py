@@ -211,3 +211,43 @@ def test_both_schedules_agree_with_the_oracle(kernel, name, monkeypatch):
         _check(a, plan.run(B.cuda(), out_dtype=torch.float16), ref)
         r = plan.run(B.cuda(), out_dtype=torch.float32, relu=True)
         assert O.scaled_max_error(r.cpu(), torch.relu(ref)) <= MAX_ERR_F32
+
+
+def test_rectangular_matrix_and_wide_features():
+    """m_rows != k_cols (the reference passes mOri and kOri separately, mGCN_online.cpp:760-800) and
+    a feature width above one slab (F = 384: three slabs of 128)."""
+    g = torch.Generator().manual_seed(2)
+    m, k = 1000, 5000
+    rows = torch.randint(0, m, (30000,), generator=g)
+    cols = torch.randint(0, k, (30000,), generator=g)
+    cols[:20000] = cols[:20000] % 24        # some dense columns -> TC blocks
+    rp, col, _ = graphs.coo_to_csr(rows, cols, m, k)
+    val = torch.randn(col.numel(), generator=g)
+    arrays, _ = O.build_format(rp, col, val)
+    assert arrays[2].numel() > 0, "the case should contain TC blocks"
+    for F in (64, 384):
+        B = torch.randn(k, F, generator=g).half()
+        ref = O.spmm_from_format(arrays, B, m)
+        plan = SpmmPlan(Format(arrays).to("cuda"), m, k)
+        _check(plan.run(B.cuda(), out_dtype=torch.float32), plan.run(B.cuda(), out_dtype=torch.float16), ref)
+    from trspmm import TrsError
+    with pytest.raises(TrsError) as e:       # a column id beyond kOri is caught before any launch
+        SpmmPlan(Format(arrays).to("cuda"), m, k - 4000)
+    assert e.value.code == -5
+
+
+def test_unaligned_feature_pointer_falls_back():
+    """B whose first row does not start on a 16-byte boundary takes the generic (plain load) path."""
+    arrays, n = _golden("rmat_s9")
+    base = torch.randn(n * 64 + 8, generator=torch.Generator().manual_seed(9)).half().cuda()
+    B = base[4:4 + n * 64].view(n, 64)      # 8-byte offset
+    assert B.data_ptr() % 16 == 8
+    ref = O.spmm_from_format(arrays, B.cpu(), n)
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    lib = plan.lib
+    from trspmm import _lib
+    out = torch.empty(n, 64, device="cuda")
+    ws = torch.empty(max(plan.workspace_bytes(64), 16), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.trs_spmm_run(plan._handle, B.data_ptr(), out.data_ptr(), 64, 0, ws.data_ptr(), ws.numel(),
+                                _lib.current_stream_ptr(out.device)))
+    assert O.scaled_max_error(out.cpu(), ref) <= MAX_ERR_F32

@@ -31,6 +31,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "trs_common.cuh"
@@ -237,6 +238,225 @@ __global__ void kb_match(const int* __restrict__ win_U, const int* __restrict__ 
     }
     win_G[w] = G;
     win_cuda_unit[w] = cuda_unit;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Matching of a HEAVY window (tens of thousands to millions of units, the hub windows of a
+// power-law graph) by one thread block.  Same result as kb_match, different execution:
+//   * the std::sort emulation runs its partitions cooperatively.  An unguarded Hoare partition
+//     swaps the k-th element >= pivot from the left with the k-th element <= pivot from the
+//     right while the former lies left of the latter; with rank(i) = how many such elements
+//     precede i, every thread can decide locally whether its element takes part and where its
+//     partner is.  K swaps happen, the cut is min(position of the (K+1)-th left stopper, position
+//     of the K-th right stopper) — checked against libstdc++ on the host, see tests;
+//   * ranges of at most kParRange elements are finished by single threads with the sequential
+//     emulation (introsort loop + the insertion pass restricted to the range);
+//   * the greedy pass stays sequential (each step depends on all earlier ones) but runs out of
+//     shared memory: a bitmask of matched units and tiles of the sorted order.
+// ---------------------------------------------------------------------------------------------
+constexpr int kHeavyUnits = 4096;
+constexpr int kParRange = 4096;
+constexpr int kHeavyThreads = 256;
+constexpr int kOrderTile = 2048;
+
+__global__ void kb_split_windows(const int* __restrict__ win_U, int W, int* __restrict__ light, int* __restrict__ heavy,
+                                 int* __restrict__ counters /* n_light, n_heavy, max heavy U */) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= W) return;
+    const int U = win_U[w];
+    if (U > kHeavyUnits) {
+        heavy[atomicAdd(&counters[1], 1)] = w;
+        atomicMax(&counters[2], U);
+    } else {
+        light[atomicAdd(&counters[0], 1)] = w;
+    }
+}
+
+__global__ void __launch_bounds__(kHeavyThreads) kb_match_heavy(
+    const int* __restrict__ win_U, const int* __restrict__ win_ub, const int* __restrict__ win_pb, int unit_min_nnz,
+    const unsigned char* __restrict__ unit_nnz, int* __restrict__ order_buf, unsigned char* __restrict__ matched_buf,
+    int* __restrict__ pair_a, int* __restrict__ pair_b, int* __restrict__ win_G, int* __restrict__ win_cuda_unit,
+    const int* __restrict__ sel, int mask_words_cap) {
+    extern __shared__ unsigned int dyn[];   // [mask_words_cap] matched bitmask, then [kOrderTile] order tile
+    __shared__ int s_stack[64][3];
+    __shared__ int s_small[kHeavyThreads][3];
+    __shared__ int s_scan[kHeavyThreads];
+    __shared__ int s_sp, s_nsmall, s_K, s_lnext, s_cur[3], s_G, s_cuda;
+    const int tid = threadIdx.x;
+    const int w = sel[blockIdx.x];
+    const int U = win_U[w];
+    const unsigned char* nnz = unit_nnz + win_ub[w];
+    int* order = order_buf + win_ub[w];
+    int* swapL = pair_a + win_pb[w];   // scratch during the sort, pair list afterwards
+    int* swapR = pair_b + win_pb[w];
+    for (int i = tid; i < U; i += kHeavyThreads) order[i] = i;
+    if (tid == 0) {
+        s_stack[0][0] = 0; s_stack[0][1] = U; s_stack[0][2] = 2 * StdSort<UnitLess>::floor_log2(U);
+        s_sp = 1; s_nsmall = 0;
+    }
+    __syncthreads();
+    StdSort<UnitLess> S(order, UnitLess{nnz});
+
+    auto block_excl_scan = [&](int v, int& total) -> int {  // exclusive scan over threads (in order)
+        s_scan[tid] = v;
+        __syncthreads();
+        for (int off = 1; off < kHeavyThreads; off <<= 1) {
+            const int t = tid >= off ? s_scan[tid - off] : 0;
+            __syncthreads();
+            s_scan[tid] += t;
+            __syncthreads();
+        }
+        total = s_scan[kHeavyThreads - 1];
+        const int ex = s_scan[tid] - v;
+        __syncthreads();
+        return ex;
+    };
+    auto run_small = [&]() {  // every thread finishes one small range
+        __syncthreads();
+        if (tid < s_nsmall) {
+            const int f = s_small[tid][0], l = s_small[tid][1], d = s_small[tid][2];
+            if (d < 0) S.heap_sort(f, l - f);
+            else { S.introsort_range(f, l, d); S.insertion_range(f, l); }
+        }
+        __syncthreads();
+        if (tid == 0) s_nsmall = 0;
+        __syncthreads();
+    };
+
+    while (true) {
+        __syncthreads();
+        const int sp_now = s_sp;   // read by everyone before thread 0 pops
+        __syncthreads();
+        if (sp_now == 0) break;
+        if (tid == 0) {
+            --s_sp;
+            s_cur[0] = s_stack[s_sp][0]; s_cur[1] = s_stack[s_sp][1]; s_cur[2] = s_stack[s_sp][2];
+        }
+        __syncthreads();
+        const int first = s_cur[0], last = s_cur[1];
+        int depth = s_cur[2];
+        if (last - first <= kParRange || depth == 0) {
+            if (last - first > 1) {
+                if (tid == 0) {
+                    s_small[s_nsmall][0] = first; s_small[s_nsmall][1] = last;
+                    s_small[s_nsmall][2] = (last - first > kParRange) ? -1 : depth;   // -1: depth exhausted -> heap sort
+                    ++s_nsmall;
+                }
+                __syncthreads();
+                if (s_nsmall == kHeavyThreads) run_small();
+            }
+            continue;
+        }
+        --depth;
+        if (tid == 0) S.move_median_to_first(first, first + 1, first + (last - first) / 2, last - 1);
+        __syncthreads();
+        const int pvk = nnz[order[first]];
+        const int lo = first + 1, n = last - lo;
+        const int chunk = (n + kHeavyThreads - 1) / kHeavyThreads;
+        const int cb = min(lo + tid * chunk, last), ce = min(cb + chunk, last);
+        // pass 1: stoppers per chunk.  left stopper: key <= pivot key (not less than the pivot in
+        // the descending order); right stopper: key >= pivot key
+        int cL = 0, cR = 0;
+        for (int i = cb; i < ce; ++i) {
+            const int k = nnz[order[i]];
+            cL += (k <= pvk);
+            cR += (k >= pvk);
+        }
+        int totL, totR;
+        const int baseL = block_excl_scan(cL, totL);
+        const int exR = block_excl_scan(cR, totR);
+        const int baseRright = totR - exR - cR;   // right stoppers in later chunks
+        // pass 2a: which left stoppers swap; K = their number
+        int lrank = baseL, rem = cR, myswaps = 0;
+        for (int i = cb; i < ce; ++i) {
+            const int k = nnz[order[i]];
+            int right_of_i = baseRright + rem;
+            if (k >= pvk) { right_of_i -= 1; rem -= 1; }
+            if (k <= pvk) {
+                ++lrank;
+                if (right_of_i >= lrank) { swapL[lrank - 1] = i; ++myswaps; }
+            }
+        }
+        int K;
+        (void)block_excl_scan(myswaps, K);
+        if (tid == 0) s_lnext = 0x7fffffff;
+        __syncthreads();
+        // pass 2b: the partners on the right, and the (K+1)-th left stopper
+        lrank = baseL; rem = cR;
+        for (int i = cb; i < ce; ++i) {
+            const int k = nnz[order[i]];
+            if (k >= pvk) {
+                const int rrank = baseRright + rem;   // rank from the right, 1-based
+                if (rrank <= K) swapR[rrank - 1] = i;
+                rem -= 1;
+            }
+            if (k <= pvk) {
+                ++lrank;
+                if (lrank == K + 1) s_lnext = i;
+            }
+        }
+        __syncthreads();
+        const int cut = min(s_lnext, K >= 1 ? swapR[K - 1] : 0x7fffffff);
+        __syncthreads();
+        for (int k = tid; k < K; k += kHeavyThreads) {
+            const int a = swapL[k], b = swapR[k];
+            const int t = order[a]; order[a] = order[b]; order[b] = t;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            s_stack[s_sp][0] = cut; s_stack[s_sp][1] = last; s_stack[s_sp][2] = depth; ++s_sp;
+            s_stack[s_sp][0] = first; s_stack[s_sp][1] = cut; s_stack[s_sp][2] = depth; ++s_sp;
+        }
+    }
+    run_small();
+
+    // ---- greedy pass (block_online.cpp:365-386), thread 0 over shared-memory tiles --------------
+    const int words = (U + 31) / 32;
+    const bool in_smem = words <= mask_words_cap;
+    unsigned int* mask = dyn;
+    int* tile = (int*)(dyn + mask_words_cap);
+    unsigned char* matched = matched_buf + win_ub[w];
+    if (in_smem) { for (int i = tid; i < words; i += kHeavyThreads) mask[i] = 0u; }
+    else { for (int i = tid; i < U; i += kHeavyThreads) matched[i] = 0; }
+    if (tid == 0) { s_G = 0; s_cuda = -1; s_cur[0] = 0; }
+    __syncthreads();
+    auto is_set = [&](int i) -> bool { return in_smem ? ((mask[i >> 5] >> (i & 31)) & 1u) != 0 : matched[i] != 0; };
+    auto set_bit = [&](int i) { if (in_smem) mask[i >> 5] |= 1u << (i & 31); else matched[i] = 1; };
+    for (int k0 = 0; k0 < U; k0 += kOrderTile) {
+        const int len = min(kOrderTile, U - k0);
+        for (int i = tid; i < len; i += kHeavyThreads) tile[i] = order[k0 + i];
+        __syncthreads();
+        if (tid == 0) {
+            int G = s_G, lowest = s_cur[0];
+            for (int k = 0; k < len; ++k) {
+                const int idx = tile[k];
+                if (is_set(idx)) continue;
+                while (lowest < U && is_set(lowest)) ++lowest;
+                int partner = lowest;
+                if (partner == idx) {
+                    ++partner;
+                    while (partner < U && is_set(partner)) ++partner;
+                }
+                if (partner >= U) continue;
+                set_bit(idx); set_bit(partner);
+                swapL[G] = idx; swapR[G] = partner;   // pair_a / pair_b of this window
+                ++G;
+            }
+            s_G = G; s_cur[0] = lowest;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int G = s_G;
+        if (U & 1) {
+            int left = 0;
+            while (is_set(left)) ++left;
+            if ((int)nnz[left] >= unit_min_nnz) { swapL[G] = left; swapR[G] = -1; ++G; }
+            else s_cuda = left;
+        }
+        win_G[w] = G;
+        win_cuda_unit[w] = s_cuda;
+    }
 }
 
 __device__ __forceinline__ int find_window(const int* __restrict__ prefix, int W, int x) {
@@ -837,9 +1057,33 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     }
 
     // ---- 6. matching -----------------------------------------------------------------------------
-    kb_match<<<grid_for(W, 64), 64, 0, st>>>(win_U, win_ub, win_pb, W, cfg.unit_min_nnz, unit_nnz, order_buf, matched,
-                                              pair_a, pair_b, win_G, win_cuda_unit, nullptr, W);
+    // light windows: one thread each; heavy windows (hubs): one block each
+    int *sel_light, *sel_heavy, *sel_cnt;
+    TRS_TRY(sc.get<int>((size_t)W + 1, &sel_light));
+    TRS_TRY(sc.get<int>((size_t)W + 1, &sel_heavy));
+    TRS_TRY(sc.get<int>(4, &sel_cnt));
+    TRS_CUDA(cudaMemsetAsync(sel_cnt, 0, 4 * sizeof(int), st));
+    kb_split_windows<<<grid_for(W), 256, 0, st>>>(win_U, W, sel_light, sel_heavy, sel_cnt);
     TRS_LAUNCH_CHECK();
+    int h_cnt[4] = {0, 0, 0, 0};
+    TRS_CUDA(cudaMemcpyAsync(h_cnt, sel_cnt, 4 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    TRS_CUDA(cudaStreamSynchronize(st));
+    if (h_cnt[0] > 0) {
+        kb_match<<<grid_for(h_cnt[0], 64), 64, 0, st>>>(win_U, win_ub, win_pb, W, cfg.unit_min_nnz, unit_nnz, order_buf,
+                                                          matched, pair_a, pair_b, win_G, win_cuda_unit, sel_light, h_cnt[0]);
+        TRS_LAUNCH_CHECK();
+    }
+    if (h_cnt[1] > 0) {
+        // shared memory: bitmask of matched units (as many words as fit) + one tile of the order
+        const int max_words = (h_cnt[2] + 31) / 32;
+        const int cap_words = std::min(max_words, (200 * 1024 - kOrderTile * 4) / 4);
+        const size_t smem = (size_t)cap_words * 4 + (size_t)kOrderTile * 4;
+        TRS_CUDA(cudaFuncSetAttribute(kb_match_heavy, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kb_match_heavy<<<h_cnt[1], kHeavyThreads, smem, st>>>(win_U, win_ub, win_pb, cfg.unit_min_nnz, unit_nnz, order_buf,
+                                                             matched, pair_a, pair_b, win_G, win_cuda_unit, sel_heavy,
+                                                             cap_words);
+        TRS_LAUNCH_CHECK();
+    }
     TRS_TRY(cub_.exclusive_sum(win_G, B->s_offset.p, W + 1));
     int G = 0;
     TRS_TRY(read_int(B->s_offset.p + W, st, &G));

@@ -129,15 +129,13 @@ struct StdSort {
         }
     }
 
-    // std::sort(a, a + n, less)
-    TRS_HD void sort(int n) {
-        if (n <= 0) return;
-        // introsort loop with an explicit stack: the recursion takes the right part and loops on
-        // the left one; the two are disjoint, so the order in which they are processed is free.
+    // std::__introsort_loop(a + first, a + last, depth): leaves ranges of <= 16 elements unsorted.
+    // The recursion takes the right part and loops on the left one; the two are disjoint, so the
+    // order in which they are processed is free and an explicit stack does.
+    TRS_HD void introsort_range(int first0, int last0, int depth0) {
         int st_first[64], st_last[64], st_depth[64];
-        int sp = 0;
-        st_first[0] = 0; st_last[0] = n; st_depth[0] = 2 * floor_log2(n);
-        sp = 1;
+        int sp = 1;
+        st_first[0] = first0; st_last[0] = last0; st_depth[0] = depth0;
         while (sp > 0) {
             --sp;
             int first = st_first[sp], last = st_last[sp], depth = st_depth[sp];
@@ -157,6 +155,17 @@ struct StdSort {
                 last = cut;
             }
         }
+    }
+
+    // What std::__final_insertion_sort does to the elements of [first, last) when that range is a
+    // union of whole partition leaves: no element moves past a leaf boundary (everything to the
+    // left of a leaf is not greater), so a guarded insertion sort of the range alone is identical.
+    TRS_HD void insertion_range(int first, int last) { insertion_sort(first, last); }
+
+    // std::sort(a, a + n, less)
+    TRS_HD void sort(int n) {
+        if (n <= 0) return;
+        introsort_range(0, n, 2 * floor_log2(n));
         if (n > 16) {
             insertion_sort(0, 16);
             for (int i = 16; i != n; ++i) unguarded_linear_insert(i);
