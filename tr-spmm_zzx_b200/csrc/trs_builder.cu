@@ -104,8 +104,15 @@ __global__ void kb_wcol_info(const u64* __restrict__ keys, const int* __restrict
     wc_col[j] = (int)((k0 >> 4) & ((1ull << col_bits) - 1ull));
     wc_count[j] = (unsigned char)count;
     wc_mask[j] = (unsigned short)mask;
-    atomicAdd(&win_ncol[w], 1);
-    if (!skip_tc && count >= density) atomicAdd(&win_ncand[w], 1);
+    // per-window counters, one atomic per warp and window (hub windows hold 10^5+ records)
+    const unsigned active = __activemask();
+    const unsigned peers = __match_any_sync(active, w);
+    const bool cand = !skip_tc && count >= density;
+    const unsigned cand_peers = __ballot_sync(active, cand) & peers;
+    if ((threadIdx.x & 31) == __ffs(peers) - 1) {
+        atomicAdd(&win_ncol[w], __popc(peers));
+        if (cand_peers) atomicAdd(&win_ncand[w], __popc(cand_peers));
+    }
     key2[j] = ((unsigned)w << 4) | (unsigned)(16 - count);
 }
 
@@ -254,25 +261,23 @@ __global__ void kb_match(const int* __restrict__ win_U, const int* __restrict__ 
 //   * the greedy pass stays sequential (each step depends on all earlier ones) but runs out of
 //     shared memory: a bitmask of matched units and tiles of the sorted order.
 // ---------------------------------------------------------------------------------------------
-constexpr int kHeavyUnits = 4096;
-constexpr int kParRange = 4096;
-constexpr int kHeavyThreads = 256;
+constexpr int kMediumUnits = 96;    // above: one warp per window
+constexpr int kHeavyUnits = 2048;    // above: one 256-thread block per window
 constexpr int kOrderTile = 2048;
 
-__global__ void kb_split_windows(const int* __restrict__ win_U, int W, int* __restrict__ light, int* __restrict__ heavy,
-                                 int* __restrict__ counters /* n_light, n_heavy, max heavy U */) {
+__global__ void kb_split_windows(const int* __restrict__ win_U, int W, int* __restrict__ light, int* __restrict__ medium,
+                                 int* __restrict__ heavy, int* __restrict__ counters /* n_light, n_medium, n_heavy, max U */) {
     int w = blockIdx.x * blockDim.x + threadIdx.x;
     if (w >= W) return;
     const int U = win_U[w];
-    if (U > kHeavyUnits) {
-        heavy[atomicAdd(&counters[1], 1)] = w;
-        atomicMax(&counters[2], U);
-    } else {
-        light[atomicAdd(&counters[0], 1)] = w;
-    }
+    if (U > kHeavyUnits) heavy[atomicAdd(&counters[2], 1)] = w;
+    else if (U > kMediumUnits) medium[atomicAdd(&counters[1], 1)] = w;
+    else light[atomicAdd(&counters[0], 1)] = w;
+    atomicMax(&counters[3], U);
 }
 
-__global__ void __launch_bounds__(kHeavyThreads) kb_match_heavy(
+template <int kHeavyThreads, int kParRange>
+__global__ void __launch_bounds__(kHeavyThreads) kb_match_coop(
     const int* __restrict__ win_U, const int* __restrict__ win_ub, const int* __restrict__ win_pb, int unit_min_nnz,
     const unsigned char* __restrict__ unit_nnz, int* __restrict__ order_buf, unsigned char* __restrict__ matched_buf,
     int* __restrict__ pair_a, int* __restrict__ pair_b, int* __restrict__ win_G, int* __restrict__ win_cuda_unit,
@@ -1057,13 +1062,14 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     }
 
     // ---- 6. matching -----------------------------------------------------------------------------
-    // light windows: one thread each; heavy windows (hubs): one block each
-    int *sel_light, *sel_heavy, *sel_cnt;
+    // small windows: one thread each; medium: one warp each; heavy (hubs): one 256-thread block each
+    int *sel_light, *sel_medium, *sel_heavy, *sel_cnt;
     TRS_TRY(sc.get<int>((size_t)W + 1, &sel_light));
+    TRS_TRY(sc.get<int>((size_t)W + 1, &sel_medium));
     TRS_TRY(sc.get<int>((size_t)W + 1, &sel_heavy));
     TRS_TRY(sc.get<int>(4, &sel_cnt));
     TRS_CUDA(cudaMemsetAsync(sel_cnt, 0, 4 * sizeof(int), st));
-    kb_split_windows<<<grid_for(W), 256, 0, st>>>(win_U, W, sel_light, sel_heavy, sel_cnt);
+    kb_split_windows<<<grid_for(W), 256, 0, st>>>(win_U, W, sel_light, sel_medium, sel_heavy, sel_cnt);
     TRS_LAUNCH_CHECK();
     int h_cnt[4] = {0, 0, 0, 0};
     TRS_CUDA(cudaMemcpyAsync(h_cnt, sel_cnt, 4 * sizeof(int), cudaMemcpyDeviceToHost, st));
@@ -1074,14 +1080,21 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
         TRS_LAUNCH_CHECK();
     }
     if (h_cnt[1] > 0) {
+        const int cap_words = (kHeavyUnits + 31) / 32;
+        const size_t smem = (size_t)cap_words * 4 + (size_t)kOrderTile * 4;
+        kb_match_coop<32, 64><<<h_cnt[1], 32, smem, st>>>(win_U, win_ub, win_pb, cfg.unit_min_nnz, unit_nnz, order_buf, matched,
+                                                          pair_a, pair_b, win_G, win_cuda_unit, sel_medium, cap_words);
+        TRS_LAUNCH_CHECK();
+    }
+    if (h_cnt[2] > 0) {
         // shared memory: bitmask of matched units (as many words as fit) + one tile of the order
-        const int max_words = (h_cnt[2] + 31) / 32;
+        const int max_words = (h_cnt[3] + 31) / 32;
         const int cap_words = std::min(max_words, (200 * 1024 - kOrderTile * 4) / 4);
         const size_t smem = (size_t)cap_words * 4 + (size_t)kOrderTile * 4;
-        TRS_CUDA(cudaFuncSetAttribute(kb_match_heavy, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kb_match_heavy<<<h_cnt[1], kHeavyThreads, smem, st>>>(win_U, win_ub, win_pb, cfg.unit_min_nnz, unit_nnz, order_buf,
-                                                             matched, pair_a, pair_b, win_G, win_cuda_unit, sel_heavy,
-                                                             cap_words);
+        TRS_CUDA(cudaFuncSetAttribute(kb_match_coop<256, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kb_match_coop<256, 1024><<<h_cnt[2], 256, smem, st>>>(win_U, win_ub, win_pb, cfg.unit_min_nnz, unit_nnz, order_buf,
+                                                              matched, pair_a, pair_b, win_G, win_cuda_unit, sel_heavy,
+                                                              cap_words);
         TRS_LAUNCH_CHECK();
     }
     TRS_TRY(cub_.exclusive_sum(win_G, B->s_offset.p, W + 1));
