@@ -181,6 +181,10 @@ typedef struct trs_build_config {
     float tc_min_util;   /* minimum nnz / (window * 8) of a kept TC chunk  */
     int32_t skip_tc;     /* LIBRA_SKIP_TC                                  */
     int32_t unit_min_nnz;/* LIBRA_SPTC_UNIT_MIN_NNZ (reference default 2)  */
+    int32_t strict;      /* 0: bit-exact with the reference, which drops the third and fourth
+                          * non-zero a row has inside one 4-column group (block_online.cpp:683-695);
+                          * 1: lossless — those entries join the row's CUDA-core part, so that the
+                          * format encodes A exactly (arrays then differ from the reference's) */
 } trs_build_config;
 
 typedef struct trs_build_stats_t {

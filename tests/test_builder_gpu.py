@@ -159,3 +159,37 @@ def test_builder_many_heavy_windows():
     want, _ = O.build_format(rp, col, val)
     fmt, _ = build_format(rp.cuda(), col.cuda(), val.cuda())
     _same(fmt, want)
+
+
+@pytest.mark.parametrize("case", [("rmat", dict(scale=12, edge_factor=16, seed=2)),
+                                  ("clustered", dict(n=2048, community=128, intra=24, glob=4, seed=3))])
+def test_strict_mode_is_lossless(case):
+    """strict=True: the TC and SPTC arrays stay as the reference builds them, and every entry the
+    reference drops re-appears in the row's CUDA-core part, so that the format encodes A exactly and
+    the SpMM equals torch.sparse A.B on every row."""
+    from trspmm import SpmmPlan
+    kind, gkw = case
+    rp, col, val = getattr(graphs, kind + "_graph")(**gkw)
+    n = rp.numel() - 1
+    compat, cst = build_format(rp.cuda(), col.cuda(), val.cuda())
+    strict, sst = build_format(rp.cuda(), col.cuda(), val.cuda(), strict=True)
+    assert cst["dropped_nnz"] > 0 and sst["dropped_nnz"] == 0
+    for name in ("t_column", "t_value", "t_binary", "s_column", "s_mask", "s_value", "s_pos", "s_packed_a",
+                 "s_packed_meta", "s_tile_column", "s_offset"):
+        assert torch.equal(getattr(compat, name), getattr(strict, name)), name
+    extra = (strict.c_value.numel() + strict.cs_value.numel()) - (compat.c_value.numel() + compat.cs_value.numel())
+    assert extra == cst["dropped_nnz"]
+    # decoding gives back exactly A
+    r, c, v = O.decode_format([a.cpu() for a in strict.arrays()])
+    rows = torch.repeat_interleave(torch.arange(n), (rp[1:] - rp[:-1]).long()).numpy()
+    full = {(int(a), int(b)): float(x) for a, b, x in zip(rows, col.numpy(), val.numpy())}
+    got = {(int(a), int(b)): float(x) for a, b, x in zip(r, c, v)}
+    assert got == full and len(r) == len(full)
+    # CSR parts keep ascending columns inside a row part
+    off, cc = strict.c_row_offset.cpu(), strict.c_column.cpu()
+    for p in range(min(off.numel() - 1, 200)):
+        seg = cc[off[p]:off[p + 1]]
+        assert bool((seg[1:] > seg[:-1]).all())
+    B = torch.randn(n, 64, generator=torch.Generator().manual_seed(0)).half()
+    out = SpmmPlan(strict, n, n).run(B.cuda(), out_dtype=torch.float32).cpu()
+    assert O.scaled_max_error(out, O.spmm_csr(rp, col, val, B)) <= 2e-5

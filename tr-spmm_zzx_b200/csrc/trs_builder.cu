@@ -45,6 +45,7 @@ struct BuildCfg {
     int part_t, part_c, short_size, density, window;
     float tc_min_util;
     int skip_tc, unit_min_nnz;
+    int strict;  // 1: lossless — entries the reference drops go to the CUDA-core parts instead
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -513,12 +514,17 @@ __global__ void kb_emit_groups(const int* __restrict__ win_pb, const int* __rest
     s_window[g] = w;
 }
 
-// one thread per (group, local row): mask byte and the first two (value, position) slots
+// one thread per (group, local row): mask byte and the first two (value, position) slots.
+// In strict mode the non-zeros beyond the second one (which the reference drops) are recorded in
+// `extra_key` / `extra_at` (key = row << 32 | column) so that they can join the row's CUDA-core part.
 __global__ void kb_emit_rows(const int* __restrict__ grp_wcol, long long total, int window,
                              const unsigned short* __restrict__ wc_mask, const int* __restrict__ wc_start,
+                             const int* __restrict__ wc_col, const int* __restrict__ s_window,
                              const int* __restrict__ edge, const float* __restrict__ val,
                              unsigned char* __restrict__ s_mask, float* __restrict__ s_value,
-                             signed char* __restrict__ s_pos, unsigned long long* __restrict__ dropped) {
+                             signed char* __restrict__ s_pos, unsigned long long* __restrict__ dropped,
+                             unsigned long long* __restrict__ extra_key, int* __restrict__ extra_at,
+                             unsigned long long* __restrict__ extra_count, int* __restrict__ row_extra, int write_arrays) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long g = i / window;
@@ -533,13 +539,20 @@ __global__ void kb_emit_rows(const int* __restrict__ grp_wcol, long long total, 
         const unsigned m = wc_mask[j];
         if (!((m >> lr) & 1u)) continue;
         mask |= 1u << p;
+        const int at = wc_start[j] + __popc(m & ((1u << lr) - 1u));
         if (slots < 2) {
-            const int at = wc_start[j] + __popc(m & ((1u << lr) - 1u));
             rv[slots] = val[edge[at]];
             rp[slots] = p;
+        } else if (extra_key) {
+            const unsigned long long k = atomicAdd(extra_count, 1ull);
+            const long long row = (long long)s_window[g] * window + lr;
+            extra_key[k] = ((unsigned long long)row << 32) | (unsigned)wc_col[j];
+            extra_at[k] = at;
+            atomicAdd(&row_extra[row], 1);
         }
         ++slots;
     }
+    if (!write_arrays) return;
     if (slots > 2) atomicAdd(dropped, (unsigned long long)(slots - 2));
     s_mask[i] = (unsigned char)mask;
     s_value[i * 2] = rv[0];
@@ -676,51 +689,58 @@ __device__ __forceinline__ void split_counts(int n, int part_c, int short_size, 
 __global__ void kb_cuda_count(int n_rows, int window, int part_c, int short_size, const int* win_cuda_unit,
                               const int* win_cb, const int* wc_begin, const int* s_idx, const int* cand,
                               const int* wc_col, const unsigned short* wc_mask, const int* wc_start,
-                              int* __restrict__ cnt /* 4 arrays of n_rows + 1 */) {
+                              const int* __restrict__ row_extra, int* __restrict__ cnt /* 4 arrays of n_rows + 1 */) {
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows) return;
     const CudaRow cr = cuda_row(r, window, win_cuda_unit, win_cb, wc_begin, s_idx, cand, wc_col, wc_mask, wc_start);
     int nl, ns, zl, zs;
-    split_counts(cr.n, part_c, short_size, nl, ns, zl, zs);
+    split_counts(cr.n + (row_extra ? row_extra[r] : 0), part_c, short_size, nl, ns, zl, zs);
     const size_t stride = (size_t)n_rows + 1;
     cnt[r] = nl; cnt[stride + r] = ns; cnt[2 * stride + r] = zl; cnt[3 * stride + r] = zs;
 }
 
+// The row's leftover entries in ascending column order: the (at most two) entries of the window's
+// rejected unit merged with the row's strict-mode extras (sorted by column beforehand).
 __global__ void kb_cuda_fill(int n_rows, int window, int part_c, int short_size, const int* win_cuda_unit,
                              const int* win_cb, const int* wc_begin, const int* s_idx, const int* b_idx,
                              const int* cand, const int* wc_col, const unsigned short* wc_mask, const int* wc_start,
                              const int* edge, const float* val, const int* __restrict__ off,
+                             const int* __restrict__ extra_off, const unsigned long long* __restrict__ extra_key,
+                             const int* __restrict__ extra_at,
                              int* c_row_offset, int* c_row, int* c_atomic, int* c_column, float* c_value,
                              int* cs_row_offset, int* cs_row, int* cs_atomic, int* cs_column, float* cs_value) {
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r == 0) { c_row_offset[0] = 0; cs_row_offset[0] = 0; }
     if (r >= n_rows) return;
     const CudaRow cr = cuda_row(r, window, win_cuda_unit, win_cb, wc_begin, s_idx, cand, wc_col, wc_mask, wc_start);
-    const int n = cr.n;
+    const int xb = extra_off ? extra_off[r] : 0, xe = extra_off ? extra_off[r + 1] : 0;
+    const int n = cr.n + (xe - xb);
     if (n <= 0) return;
     const int w = r / window;
     const int base_atomic = (b_idx[wc_begin[w + 1]] - b_idx[wc_begin[w]]) > 0 ? 1 : 0;
     const size_t stride = (size_t)n_rows + 1;
     int pl = off[r], ps = off[stride + r], zl = off[2 * stride + r], zs = off[3 * stride + r];
-    auto put = [&](int atomic, int o, int cnt, bool residue) {
-        if (residue) {
-            for (int i = 0; i < cnt; ++i) { cs_column[zs + i] = cr.cols[o + i]; cs_value[zs + i] = val[edge[cr.at[o + i]]]; }
-            zs += cnt;
-            cs_row[ps] = r; cs_atomic[ps] = atomic; cs_row_offset[ps + 1] = zs;
-            ++ps;
-        } else {
-            for (int i = 0; i < cnt; ++i) { c_column[zl + i] = cr.cols[o + i]; c_value[zl + i] = val[edge[cr.at[o + i]]]; }
-            zl += cnt;
-            c_row[pl] = r; c_atomic[pl] = atomic; c_row_offset[pl + 1] = zl;
-            ++pl;
-        }
+    int iu = 0, ix = xb;  // cursors of the two sorted sources
+    auto next = [&](int& c, float& v) {
+        const int xc = ix < xe ? (int)(extra_key[ix] & 0xffffffffull) : 0x7fffffff;
+        if (iu < cr.n && cr.cols[iu] < xc) { c = cr.cols[iu]; v = val[edge[cr.at[iu]]]; ++iu; }
+        else { c = xc; v = val[edge[extra_at[ix]]]; ++ix; }
     };
-    if (n <= short_size) { put(base_atomic, 0, n, true); return; }
-    if (n <= part_c) { put(base_atomic, 0, n, false); return; }
-    int o = 0;
-    for (int i = 0; i < n / part_c; ++i) { put(1, o, part_c, false); o += part_c; }
+    auto put = [&](int atomic, int cnt, bool residue) {
+        for (int i = 0; i < cnt; ++i) {
+            int c; float v;
+            next(c, v);
+            if (residue) { cs_column[zs + i] = c; cs_value[zs + i] = v; }
+            else { c_column[zl + i] = c; c_value[zl + i] = v; }
+        }
+        if (residue) { zs += cnt; cs_row[ps] = r; cs_atomic[ps] = atomic; cs_row_offset[ps + 1] = zs; ++ps; }
+        else { zl += cnt; c_row[pl] = r; c_atomic[pl] = atomic; c_row_offset[pl + 1] = zl; ++pl; }
+    };
+    if (n <= short_size) { put(base_atomic, n, true); return; }
+    if (n <= part_c) { put(base_atomic, n, false); return; }
+    for (int i = 0; i < n / part_c; ++i) put(1, part_c, false);
     const int residue = n % part_c;
-    if (residue > 0) put(1, o, residue, residue <= short_size);
+    if (residue > 0) put(1, residue, residue <= short_size);
 }
 
 __global__ void kb_tiles(const int* __restrict__ tile_off, const int* __restrict__ s_offset, int W, int T,
@@ -1117,9 +1137,41 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
                                                       pair_a, pair_b, cand, wc_col, B->s_column.p, B->s_window.p, grp_wcol);
         TRS_LAUNCH_CHECK();
         kb_emit_rows<<<grid_for((long long)G * window), 256, 0, st>>>(grp_wcol, (long long)G * window, window, wc_mask,
-                                                                       wc_start, edge, val, B->s_mask.p, B->s_value.p,
-                                                                       B->s_pos.p, d_dropped);
+                                                                       wc_start, wc_col, B->s_window.p, edge, val,
+                                                                       B->s_mask.p, B->s_value.p, B->s_pos.p, d_dropped,
+                                                                       nullptr, nullptr, nullptr, nullptr, 1);
         TRS_LAUNCH_CHECK();
+    }
+    // strict mode: collect what was dropped, ordered by (row, column)
+    int* row_extra = nullptr;
+    int* extra_off = nullptr;
+    unsigned long long* extra_key = nullptr;
+    int* extra_at = nullptr;
+    if (cfg.strict && G > 0) {
+        unsigned long long h_dropped = 0;
+        TRS_CUDA(cudaMemcpyAsync(&h_dropped, d_dropped, sizeof(h_dropped), cudaMemcpyDeviceToHost, st));
+        TRS_CUDA(cudaStreamSynchronize(st));
+        if (h_dropped > 0) {
+            unsigned long long *key_a, *key_b, *d_xcount;
+            int *at_a, *at_b;
+            TRS_TRY(sc.get<unsigned long long>(h_dropped, &key_a));
+            TRS_TRY(sc.get<unsigned long long>(h_dropped, &key_b));
+            TRS_TRY(sc.get<int>(h_dropped, &at_a));
+            TRS_TRY(sc.get<int>(h_dropped, &at_b));
+            TRS_TRY(sc.get<unsigned long long>(1, &d_xcount));
+            TRS_TRY(sc.get<int>((size_t)n + 1, &row_extra));
+            TRS_TRY(sc.get<int>((size_t)n + 1, &extra_off));
+            TRS_CUDA(cudaMemsetAsync(d_xcount, 0, sizeof(unsigned long long), st));
+            TRS_CUDA(cudaMemsetAsync(row_extra, 0, sizeof(int) * ((size_t)n + 1), st));
+            kb_emit_rows<<<grid_for((long long)G * window), 256, 0, st>>>(grp_wcol, (long long)G * window, window, wc_mask,
+                                                                           wc_start, wc_col, B->s_window.p, edge, val, nullptr,
+                                                                           nullptr, nullptr, nullptr, key_a, at_a, d_xcount,
+                                                                           row_extra, 0);
+            TRS_LAUNCH_CHECK();
+            TRS_TRY(cub_.sort_pairs(key_a, key_b, at_a, at_b, (long long)h_dropped, 32 + bits_for(n), &extra_key, &extra_at));
+            TRS_TRY(cub_.exclusive_sum(row_extra, extra_off, (long long)n + 1));
+            TRS_CUDA(cudaMemsetAsync(d_dropped, 0, sizeof(unsigned long long), st));   // nothing is lost in this mode
+        }
     }
 
     // ---- 8. TC blocks, values, parts ------------------------------------------------------------
@@ -1161,7 +1213,7 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     TRS_TRY(sc.get<int>(4 * stride, &off4));
     TRS_CUDA(cudaMemsetAsync(cnt4, 0, sizeof(int) * 4 * stride, st));
     kb_cuda_count<<<grid_for(n), 256, 0, st>>>(n, window, cfg.part_c, cfg.short_size, win_cuda_unit, win_cb, wc_begin, s_idx,
-                                                cand, wc_col, wc_mask, wc_start, cnt4);
+                                                cand, wc_col, wc_mask, wc_start, row_extra, cnt4);
     TRS_LAUNCH_CHECK();
     int tot[4] = {0, 0, 0, 0};
     for (int i = 0; i < 4; ++i) {
@@ -1181,7 +1233,8 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     TRS_TRY(B->cs_column.alloc(tot[3]));
     TRS_TRY(B->cs_value.alloc(tot[3]));
     kb_cuda_fill<<<grid_for(n), 256, 0, st>>>(n, window, cfg.part_c, cfg.short_size, win_cuda_unit, win_cb, wc_begin, s_idx,
-                                               b_idx, cand, wc_col, wc_mask, wc_start, edge, val, off4, B->c_row_offset.p,
+                                               b_idx, cand, wc_col, wc_mask, wc_start, edge, val, off4, extra_off, extra_key,
+                                               extra_at, B->c_row_offset.p,
                                                B->c_row.p, B->c_atomic.p, B->c_column.p, B->c_value.p, B->cs_row_offset.p,
                                                B->cs_row.p, B->cs_atomic.p, B->cs_column.p, B->cs_value.p);
     TRS_LAUNCH_CHECK();
@@ -1257,7 +1310,7 @@ extern "C" int trs_build_create(const int32_t* rowptr, const int32_t* col, const
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return TRS_E_NO_DEVICE;
     trs_builder* B = new trs_builder();
     B->cfg = BuildCfg{cfg->part_t, cfg->part_c, cfg->short_size, cfg->density, cfg->window, cfg->tc_min_util,
-                      cfg->skip_tc, cfg->unit_min_nnz};
+                      cfg->skip_tc, cfg->unit_min_nnz, cfg->strict ? 1 : 0};
     B->n_rows = n_rows;
     B->W = ceil_div(n_rows, cfg->window);
     cudaStream_t st = (cudaStream_t)stream;

@@ -37,7 +37,8 @@ class TrsFormat(C.Structure):
 
 class TrsBuildConfig(C.Structure):
     _fields_ = [("part_t", C.c_int32), ("part_c", C.c_int32), ("short_size", C.c_int32), ("density", C.c_int32),
-                ("window", C.c_int32), ("tc_min_util", C.c_float), ("skip_tc", C.c_int32), ("unit_min_nnz", C.c_int32)]
+                ("window", C.c_int32), ("tc_min_util", C.c_float), ("skip_tc", C.c_int32), ("unit_min_nnz", C.c_int32),
+                ("strict", C.c_int32)]
 
 
 class TrsBuildStats(C.Structure):

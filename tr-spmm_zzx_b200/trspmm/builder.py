@@ -48,9 +48,11 @@ def env_switches():
 
 def build_format(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, part_t: int = 32, part_c: int = 32,
                  short_size: int = 3, density: int = 8, window: int = 16, tc_min_util: float = 0.0,
-                 skip_tc: bool | None = None, unit_min_nnz: int | None = None):
+                 skip_tc: bool | None = None, unit_min_nnz: int | None = None, strict: bool = False):
     """Build on the GPU.  Inputs: CUDA int32 row pointers / columns (canonical CSR) and fp32 values.
-    Returns (Format on the same device, stats dict)."""
+    Returns (Format on the same device, stats dict).  strict=True builds a lossless format: the
+    entries the reference drops (third / fourth non-zero of a row inside a 4-column group) go to the
+    row's CUDA-core part; those arrays are then no longer bit-identical to the reference's."""
     dev = rowptr.device
     if dev.type != "cuda":
         raise ValueError("build_format needs CUDA tensors (there is no CPU fallback)")
@@ -62,7 +64,7 @@ def build_format(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, par
     e_skip, e_min = env_switches()
     cfg = _lib.TrsBuildConfig(part_t, part_c, short_size, density, window, float(tc_min_util),
                               int(e_skip if skip_tc is None else skip_tc),
-                              int(e_min if unit_min_nnz is None else unit_min_nnz))
+                              int(e_min if unit_min_nnz is None else unit_min_nnz), int(bool(strict)))
     lib = _lib.load()
     handle = C.c_void_p()
     with torch.cuda.device(dev):
