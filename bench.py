@@ -429,7 +429,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
-    ap.add_argument("--gather", default="h1", choices=["h1", "z2"], help="gcn: which matrix the ranks exchange")
+    ap.add_argument("--gather", default="h1", choices=["h1", "z2", "fused"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

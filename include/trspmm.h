@@ -108,6 +108,17 @@ int trs_spmm_run(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, i
 #define TRS_EPILOGUE_RELU 1
 int trs_spmm_run_ex(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype, int flags,
                     void* workspace, size_t workspace_bytes, void* stream);
+/* SpMM fused with the exchange that follows it in a sharded GCN layer (no counterpart in the
+ * reference, which has neither layers nor multi-GPU code).  The plan covers this GPU's row range of
+ * a matrix with N_total rows; the fp16 result rows (ReLU optional) are written straight from the
+ * kernel's epilogue into n_dst (<= 8) buffers of shape [N_total, F] at rows row0 + local row:
+ * this GPU's copy and its NVLink peers' copies (peer-mapped device pointers, e.g. from CUDA IPC or
+ * torch symmetric memory), as plain 16-byte stores of whole 256-byte row segments.  When every
+ * rank has run it and the ranks have synchronised, each holds the whole matrix: the all-gather is
+ * gone.  Needs F % 8 == 0 and 16-byte aligned buffers. */
+int trs_spmm_run_bcast(const trs_spmm_plan* plan, const trs_half* B, void* const* dst, int n_dst,
+                       long long row0, int F, int flags, void* workspace, size_t workspace_bytes,
+                       void* stream);
 /* Health word of the plan's kernels: 0, or non-zero when a bounded pipeline wait inside a kernel
  * gave up (the affected call's output is then incomplete).  Synchronises the device. */
 int trs_spmm_status(const trs_spmm_plan* plan, int* status);

@@ -77,8 +77,14 @@ def _worker(rank, world, port, q):
         cuts = shard.balanced_window_cuts(rp, world)
         full = torch.zeros(n, 16)
         full[r0:r1] = mine
-        for src in range(world):
-            dist.broadcast(full[cuts[src]:cuts[src + 1]], src=src)
+        ops = []
+        for peer in range(world):  # unequal-count all-gather as one batch of sends / receives
+            if peer == rank:
+                continue
+            ops.append(dist.P2POp(dist.irecv, full[cuts[peer]:cuts[peer + 1]], peer))
+            ops.append(dist.P2POp(dist.isend, full[r0:r1], peer))
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
         if rank == 0:
             whole, _ = O.build_format(rp, col, val)
             q.put(bool(torch.equal(full, O.spmm_from_format(whole, B, n))))

@@ -251,3 +251,19 @@ def test_unaligned_feature_pointer_falls_back():
     _lib.check(lib.trs_spmm_run(plan._handle, B.data_ptr(), out.data_ptr(), 64, 0, ws.data_ptr(), ws.numel(),
                                 _lib.current_stream_ptr(out.device)))
     assert O.scaled_max_error(out.cpu(), ref) <= MAX_ERR_F32
+
+
+def test_bcast_epilogue_single_gpu():
+    """trs_spmm_run_bcast with two destination buffers on one GPU: both receive the fp16 rows (with
+    ReLU) at the requested row offset, identical to the ordinary entry; rows outside stay untouched."""
+    arrays, n = _golden("clustered_n512")
+    B = torch.randn(n, 128, generator=torch.Generator().manual_seed(3)).half().cuda()
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    want = plan.run(B, out_dtype=torch.float16, relu=True)
+    row0, total = 48, n + 100
+    bufs = [torch.full((total, 128), -7.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+    plan.run_bcast(B, [b.data_ptr() for b in bufs], row0, relu=True)
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert torch.equal(b[row0:row0 + n], want)
+        assert float(b[:row0].max()) == -7.0 and float(b[row0 + n:].min()) == -7.0

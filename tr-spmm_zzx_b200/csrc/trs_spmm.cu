@@ -69,6 +69,9 @@ struct KernelArgs {
     int* status;                   // device word: non-zero after a pipeline wait gave up
     int m_rows, k_cols, window, F, out_half;
     int relu;                      // 1: C = max(A'B, 0) (GCN layer epilogue)
+    void* peers[8];                // fused exchange: the fp16 rows are written into every one of these
+    int n_peers;                   //   [N_total, F] buffers (this GPU's and its NVLink peers'), 0 = off
+    long long peer_row0;           //   at global row peer_row0 + local row
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -152,8 +155,8 @@ __global__ void k_check_sorted(const int* __restrict__ a, int n, int* err) {
 // CSR remainder parts of the window (first item only) and the single write of the item's result:
 // C rows (fp32 or fp16) or, for a slice of a split window, fp32 partial sums in scratch.
 // Accumulators are in mma fragment layout: acc[n][2h + i] = row g + 8h, feature fcol + 8n + i.
-__device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
-                                            int wid, int g, int t) {
+__device__ __forceinline__ void add_csr_parts(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
+                                              int wid, int g, int t) {
     const int w = it.window;
     const size_t F = (size_t)a.F;
     // ---- CSR remainder parts: added by the first item of the window --------------------------
@@ -186,7 +189,13 @@ __device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, 
             }
         }
     }
+}
 
+__device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
+                                            int wid, int g, int t) {
+    const int w = it.window;
+    const size_t F = (size_t)a.F;
+    add_csr_parts(acc, it, a, fbase, wid, g, t);
     // ---- epilogue ----------------------------------------------------------------------------
     const int fcol = fbase + wid * 32 + 2 * t;
     if (it.slot >= 0) {
@@ -233,6 +242,40 @@ __device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, 
                 }
             }
         }
+    }
+}
+
+// Fused exchange epilogue (fp16 rows into several [N_total, F] buffers, e.g. the hidden matrix of a
+// GCN layer on every GPU of the box): the accumulators are converted once, staged as a 16 x FS
+// fp16 tile in shared memory, and each thread then writes 16-byte pieces of whole rows to every
+// destination — 256-byte contiguous row segments, which is what NVLink peer stores want.
+// `tile` must hold 16 * (FS * 2 + 16) bytes and be free (pipeline drained, block synchronised).
+template <int FS, int THREADS>
+__device__ __forceinline__ void finish_item_bcast(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
+                                                  int wid, int g, int t, unsigned char* tile) {
+    constexpr int PITCH = FS * 2 + 16;
+    if (a.relu) {
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][i] = fmaxf(acc[n][i], 0.f);
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            *(__half2*)(tile + (g + 8 * h) * PITCH + (wid * 32 + n * 8 + 2 * t) * 2) =
+                __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]);
+    __syncthreads();
+    constexpr int CPR = FS / 8;
+    for (int c = threadIdx.x; c < 16 * CPR; c += THREADS) {
+        const int lr = c / CPR, ch = c % CPR;
+        const int f = fbase + ch * 8;
+        const long long row = (long long)it.window * a.window + lr;
+        if (lr >= a.window || row >= a.m_rows || f >= a.F) continue;
+        const uint4 v = *(const uint4*)(tile + lr * PITCH + ch * 16);
+        const size_t off = (size_t)(a.peer_row0 + row) * (size_t)a.F + f;
+        for (int d = 0; d < a.n_peers; ++d) *(uint4*)((__half*)a.peers[d] + off) = v;
     }
 }
 
@@ -535,6 +578,12 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArg
         }
     }
     cp_async_wait<0>();
+    if (a.n_peers > 0 && it.slot < 0) {
+        __syncthreads();  // every warp is done with the pipeline buffers
+        add_csr_parts(acc, it, a, fbase, wid, g, t);
+        finish_item_bcast<T::FS, T::THREADS>(acc, it, a, fbase, wid, g, t, smem);
+        return;
+    }
     finish_item(acc, it, a, fbase, wid, g, t);
 }
 
@@ -990,8 +1039,14 @@ __global__ void k_window_steps(trs_format f, WindowRanges wr, int W, int* __rest
 }
 
 // Adds the partial sums of a split window in slot order and writes its 16 rows of C.
+struct PeerDst {
+    void* ptr[8];
+    int n;
+    long long row0;
+};
+
 __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __restrict__ scratch, void* C, int F,
-                               int m_rows, int window, int out_half, int relu) {
+                               int m_rows, int window, int out_half, int relu, PeerDst pd) {
     const Heavy h = heavy[blockIdx.x];
     const int per = 16 * F;
     for (int i = threadIdx.x; i < per; i += blockDim.x) {
@@ -1001,7 +1056,9 @@ __global__ void k_reduce_heavy(const Heavy* __restrict__ heavy, const float* __r
         float s = 0.f;
         for (int sl = h.slot_begin; sl < h.slot_end; ++sl) s += scratch[(size_t)sl * per + i];
         if (relu) s = fmaxf(s, 0.f);
-        if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
+        if (pd.n > 0) {
+            for (int d = 0; d < pd.n; ++d) ((__half*)pd.ptr[d])[(size_t)(pd.row0 + row) * F + f] = __float2half_rn(s);
+        } else if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
         else ((float*)C)[(size_t)row * F + f] = s;
     }
 }
@@ -1368,15 +1425,26 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
 }
 
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
-                    size_t workspace_bytes, void* stream, bool items_only);
+                    size_t workspace_bytes, void* stream, bool items_only, void* const* peers = nullptr, int n_peers = 0,
+                    long long peer_row0 = 0);
 
 extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
                                void* workspace, size_t workspace_bytes, void* stream) {
     return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, false);
 }
 
+extern "C" int trs_spmm_run_bcast(const trs_spmm_plan* p, const trs_half* B, void* const* dst, int n_dst, long long row0,
+                                  int F, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!p || !dst || n_dst < 1 || n_dst > 8 || row0 < 0) return TRS_E_ARG;
+    for (int d = 0; d < n_dst; ++d)
+        if (!dst[d] || ((uintptr_t)dst[d] & 15)) return TRS_E_ARG;
+    if (F % 8 != 0 || ((uintptr_t)B & 15) || !p->arrays_aligned) return TRS_E_ARG;  // the 16-byte row pieces need it
+    return run_impl(p, B, dst[0], F, TRS_OUT_F16, flags, workspace, workspace_bytes, stream, /*items_only=*/true, dst, n_dst, row0);
+}
+
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
-                    size_t workspace_bytes, void* stream, bool items_only) {
+                    size_t workspace_bytes, void* stream, bool items_only, void* const* peers, int n_peers,
+                    long long peer_row0) {
     if (!p || !B || !C || F <= 0) return TRS_E_ARG;
     if (flags & ~TRS_EPILOGUE_RELU) return TRS_E_ARG;
     if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
@@ -1390,6 +1458,8 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
     a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
+    a.n_peers = n_peers; a.peer_row0 = peer_row0;
+    for (int d = 0; d < 8; ++d) a.peers[d] = d < n_peers ? peers[d] : nullptr;
     a.tc_dense = p->tc_dense.p; a.zeros = p->zeros.p; a.status = (int*)(p->zeros.p + 512);
     int rc;
     if (flat) {
@@ -1397,7 +1467,7 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
         if (F <= 64) return launch_flat_kernel<2>(p, a, st);
         return launch_flat_kernel<4>(p, a, st);
     }
-    const bool bulk = p->bulk_ok && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
+    const bool bulk = p->bulk_ok && n_peers == 0 && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
     if (bulk) {
         if (F <= 32) rc = launch_bulk_kernel<1>(a, p->n_items, st);
         else if (F <= 64) rc = launch_bulk_kernel<2>(a, p->n_items, st);
@@ -1407,7 +1477,10 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     else rc = launch_window_kernel<4>(a, p->n_items, p->arrays_aligned, st);
     if (rc) return rc;
     if (p->n_heavy > 0) {
-        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half, a.relu);
+        PeerDst pd;
+        pd.n = a.n_peers; pd.row0 = a.peer_row0;
+        for (int d = 0; d < 8; ++d) pd.ptr[d] = a.peers[d];
+        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half, a.relu, pd);
         TRS_LAUNCH_CHECK();
     }
     return TRS_OK;

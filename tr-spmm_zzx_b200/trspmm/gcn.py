@@ -6,7 +6,7 @@ configuration:  H1 = ReLU(A (X W1)),  out = A (H1 W2)  with fp16 activations and
 accumulation.  The dense products run first because they shrink the feature width before the
 SpMM; they go through torch.matmul (a plain library GEMM).  The SpMMs, the fused ReLU and the
 down-conversion are this library's kernel; ranks exchange their row blocks of the hidden matrix
-with NCCL broadcasts (window-aligned blocks of different sizes) between the layers.
+(window-aligned, different sizes) with one grouped batch of NCCL sends / receives between the layers.
 """
 from __future__ import annotations
 
@@ -27,26 +27,47 @@ class ShardedGCN2:
         self.fmt, self.stats = build_format(rp_l, col_l, val_l, window=window)
         self.plan = SpmmPlan(self.fmt, max(self.r1 - self.r0, 1), self.n, window)
         self.gather_bytes = 0
+        self._symm = {}   # feature width -> (tensor, handle) of the peer-mapped hidden matrix
+
+    def _symmetric(self, F: int, device):
+        """A [N, F] fp16 matrix every rank of the box can store into (torch symmetric memory)."""
+        if F not in self._symm:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            t = symm_mem.empty((self.n, F), dtype=torch.float16, device=device)
+            hdl = symm_mem.rendezvous(t, group=self.group if self.group is not None else dist.group.WORLD)
+            self._symm[F] = (t, hdl)
+        return self._symm[F]
 
     def _exchange(self, full: torch.Tensor):
-        """Every rank's rows [cuts[r], cuts[r+1]) of `full` become valid on all ranks."""
+        """Every rank's rows [cuts[r], cuts[r+1]) of `full` become valid on all ranks.  The blocks
+        are window-aligned and of different sizes, so this is an all-gather with unequal counts:
+        one batch of point-to-point sends / receives that NCCL runs as a single group, every
+        NVLink direction busy at once."""
         if self.world == 1:
             return
         import torch.distributed as dist
-        works = []
-        for src in range(self.world):
-            a, b = self.cuts[src], self.cuts[src + 1]
+        ops = []
+        a, b = self.cuts[self.rank], self.cuts[self.rank + 1]
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            pa, pb = self.cuts[peer], self.cuts[peer + 1]
+            if pb > pa:
+                ops.append(dist.P2POp(dist.irecv, full[pa:pb], peer, self.group))
+                self.gather_bytes += (pb - pa) * full.shape[1] * full.element_size()
             if b > a:
-                works.append(dist.broadcast(full[a:b], src=src, group=self.group, async_op=True))
-                if src != self.rank:
-                    self.gather_bytes += (b - a) * full.shape[1] * full.element_size()
-        for w in works:
-            w.wait()
+                ops.append(dist.P2POp(dist.isend, full[a:b], peer, self.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
 
     def forward(self, X: torch.Tensor, W1: torch.Tensor, W2: torch.Tensor, gather: str = "h1") -> torch.Tensor:
         """X [N, F0] fp16 (replicated), W1 [F0, F1], W2 [F1, F2] fp16.  Returns this rank's rows of
-        the output, [r1 - r0, F2] fp16.  gather="h1" exchanges the hidden matrix (N x F1);
-        gather="z2" multiplies the own rows by W2 first and exchanges N x F2 instead."""
+        the output, [r1 - r0, F2] fp16.  gather="h1" exchanges the hidden matrix (N x F1) with NCCL;
+        gather="z2" multiplies the own rows by W2 first and exchanges N x F2 instead;
+        gather="fused" lets the layer-1 SpMM store its rows into every rank's H1 itself
+        (peer-mapped symmetric memory, trs_spmm_run_bcast)."""
         self.gather_bytes = 0
         r0, r1 = self.r0, self.r1
         z1 = torch.matmul(X, W1)                                   # [N, F1], replicated compute
@@ -56,6 +77,20 @@ class ShardedGCN2:
                 self.plan.run(z1, out=h1[r0:r1], relu=True)        # ReLU + fp16 fused into the one write
             self._exchange(h1)
             z2 = torch.matmul(h1, W2)                              # [N, F2]
+        elif gather == "fused":
+            # layer-1 SpMM writes its rows (ReLU, fp16) into every rank's copy of H1 over NVLink from
+            # the kernel's epilogue: no separate all-gather, the exchange overlaps the SpMM
+            if self.world == 1:
+                h1 = torch.empty((self.n, W1.shape[1]), dtype=torch.float16, device=X.device)
+                self.plan.run(z1, out=h1[r0:r1], relu=True)
+            else:
+                h1, hdl = self._symmetric(W1.shape[1], X.device)
+                hdl.barrier(channel=0)                 # everyone is done reading the previous H1
+                if r1 > r0:
+                    self.plan.run_bcast(z1, [int(p) for p in hdl.buffer_ptrs], r0, relu=True)
+                    self.gather_bytes += (self.n - (r1 - r0)) * W1.shape[1] * 2
+                hdl.barrier(channel=1)                 # all rows of all ranks have landed
+            z2 = torch.matmul(h1, W2)
         elif gather == "z2":
             h1_local = self.plan.run(z1, relu=True) if r1 > r0 else z1[:0]
             z2 = torch.empty((self.n, W2.shape[1]), dtype=torch.float16, device=X.device)
@@ -63,5 +98,5 @@ class ShardedGCN2:
                 torch.matmul(h1_local[: r1 - r0], W2, out=z2[r0:r1])
             self._exchange(z2)
         else:
-            raise ValueError("gather must be 'h1' or 'z2'")
+            raise ValueError("gather must be 'h1', 'z2' or 'fused'")
         return self.plan.run(z2)[: r1 - r0] if r1 > r0 else z2[:0]

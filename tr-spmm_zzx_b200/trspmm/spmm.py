@@ -82,6 +82,23 @@ class SpmmPlan:
                                                 _lib.current_stream_ptr(self.device)))
         return out
 
+    def run_bcast(self, B: torch.Tensor, dst_ptrs, row0: int, relu: bool = False):
+        """trs_spmm_run_bcast: the fp16 result rows go straight from the kernel's epilogue into every
+        buffer of `dst_ptrs` (device pointers of [N_total, F] fp16 matrices: this GPU's and its
+        NVLink peers') at rows row0 + local row.  Asynchronous on the current stream."""
+        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
+            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
+        F = B.shape[1]
+        ws = self._ws.get(F)
+        if ws is None:
+            ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
+            self._ws[F] = ws
+        arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.trs_spmm_run_bcast(self._handle, B.data_ptr(), arr, len(dst_ptrs), int(row0), F,
+                                                   1 if relu else 0, ws.data_ptr(), ws.numel(),
+                                                   _lib.current_stream_ptr(self.device)))
+
     def run_static(self, B: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """trs_spmm_run_static: the same product with the partial sums of split windows kept in
         the library's fixed device array, for callers that may not allocate device memory (the
