@@ -404,6 +404,9 @@ def run_gcn(args, rank, world, local_rank):
         ms = t[0:1].clone(); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         k = t[1:2].clone(); dist.all_reduce(k, op=dist.ReduceOp.SUM)
         t = torch.cat([ms, k])
+    model.profile = True
+    model.forward(X, W1, W2, gather=args.gather)
+    breakdown = {k: round(v, 3) for k, v in model.last_breakdown.items()}
     if rank == 0:
         ms, kept_total = float(t[0]), float(t[1])
         flops = 2.0 * kept_total * (128 + 64) + 2.0 * n * (256 * 128 + 128 * 64)
@@ -413,7 +416,8 @@ def run_gcn(args, rank, world, local_rank):
                           "dtype": "f16 in / f32 accumulate", "data": "synthetic",
                           "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather,
                                      "n_rows": n, "nnz": nnz, "kept_nnz": int(kept_total),
-                                     "gather_bytes_received_rank0": model.gather_bytes}}), flush=True)
+                                     "gather_bytes_received_rank0": model.gather_bytes,
+                                     "stage_ms_rank0": breakdown}}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

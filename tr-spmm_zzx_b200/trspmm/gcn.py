@@ -27,6 +27,8 @@ class ShardedGCN2:
         self.fmt, self.stats = build_format(rp_l, col_l, val_l, window=window)
         self.plan = SpmmPlan(self.fmt, max(self.r1 - self.r0, 1), self.n, window)
         self.gather_bytes = 0
+        self.profile = False
+        self.last_breakdown = {}
         self._symm = {}   # feature width -> (tensor, handle) of the peer-mapped hidden matrix
 
     def _symmetric(self, F: int, device):
@@ -70,13 +72,26 @@ class ShardedGCN2:
         (peer-mapped symmetric memory, trs_spmm_run_bcast)."""
         self.gather_bytes = 0
         r0, r1 = self.r0, self.r1
+        marks = []
+
+        def mark(name):
+            if self.profile:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+
+        mark("start")
         z1 = torch.matmul(X, W1)                                   # [N, F1], replicated compute
+        mark("gemm1")
         if gather == "h1":
             h1 = torch.empty((self.n, W1.shape[1]), dtype=torch.float16, device=X.device)
             if r1 > r0:
                 self.plan.run(z1, out=h1[r0:r1], relu=True)        # ReLU + fp16 fused into the one write
+            mark("spmm1")
             self._exchange(h1)
+            mark("exchange")
             z2 = torch.matmul(h1, W2)                              # [N, F2]
+            mark("gemm2")
         elif gather == "fused":
             # layer-1 SpMM writes its rows (ReLU, fp16) into every rank's copy of H1 over NVLink from
             # the kernel's epilogue: no separate all-gather, the exchange overlaps the SpMM
@@ -90,13 +105,22 @@ class ShardedGCN2:
                     self.plan.run_bcast(z1, [int(p) for p in hdl.buffer_ptrs], r0, relu=True)
                     self.gather_bytes += (self.n - (r1 - r0)) * W1.shape[1] * 2
                 hdl.barrier(channel=1)                 # all rows of all ranks have landed
+            mark("spmm1+exchange")
             z2 = torch.matmul(h1, W2)
+            mark("gemm2")
         elif gather == "z2":
             h1_local = self.plan.run(z1, relu=True) if r1 > r0 else z1[:0]
             z2 = torch.empty((self.n, W2.shape[1]), dtype=torch.float16, device=X.device)
             if r1 > r0:
                 torch.matmul(h1_local[: r1 - r0], W2, out=z2[r0:r1])
+            mark("spmm1+gemm2")
             self._exchange(z2)
+            mark("exchange")
         else:
             raise ValueError("gather must be 'h1', 'z2' or 'fused'")
-        return self.plan.run(z2)[: r1 - r0] if r1 > r0 else z2[:0]
+        out = self.plan.run(z2)[: r1 - r0] if r1 > r0 else z2[:0]
+        mark("spmm2")
+        if self.profile:
+            torch.cuda.synchronize()
+            self.last_breakdown = {n: marks[i][1].elapsed_time(e) for i, (n, e) in enumerate(marks[1:])}
+        return out
