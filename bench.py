@@ -129,6 +129,12 @@ def make_matrix(workload, device):
     return rp, col, val, F
 
 
+# DRAM bytes of one launch of the window kernel on one GPU (dram__bytes_read.sum +
+# dram__bytes_write.sum of single-metric, one-pass ncu captures of this very command; the
+# summaries under profiles/ give the commands).  Workloads not captured report null.
+MEASURED_TRAFFIC = {("rmat21", 128): 8.29e9 + 0.628e9, ("rmat20", 128): 1.728e9 + 0.269e9}
+
+
 def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):
     """Canonical-CSR traffic of one SpMM: fp16 value + int32 column per entry, row pointers,
     every B row once, every C element once."""
@@ -307,7 +313,10 @@ def run_ours(args, rank, world, local_rank):
                        "build_ms_rank0": st["build_ms"], "tiles_rank0": st["tiles"], "tc_blocks_rank0": st["tc_blocks"]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "algorithmic_bytes_per_step_rank0": alg_rank,
-                         "algorithmic_bytes_per_step_job": alg_job, "traffic": None, "kernel": "k_window_spmm"},
+                         "algorithmic_bytes_per_step_job": alg_job,
+                         "traffic": MEASURED_TRAFFIC.get((args.workload, F)) if world == 1 else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch (profiles/)",
+                         "kernel": "k_window_spmm_lean"},
             "e2e": {"value": 2.0 * kept_total * F / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": n * F * 2, "d2h_bytes_per_step": max(m_local, 1) * F * 2,
                     "h2d_ms": h2d / e2e_steps, "d2h_ms": d2h / e2e_steps,
