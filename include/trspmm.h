@@ -139,6 +139,13 @@ int trs_spmm_status(const trs_spmm_plan* plan, int* status);
 int trs_spmm_run_static(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
                         void* stream);
 int trs_spmm_static_scratch_bytes(const trs_spmm_plan* plan, int F, size_t* bytes);
+/* trs_spmm_run_ex restricted to the row windows [window_begin, window_end) of the plan: only the
+ * rows of those windows are written.  Lets a caller pipeline a large SpMM against whatever
+ * consumes its rows (a device->host copy, an exchange).  No counterpart in the reference. */
+int trs_spmm_run_windows(const trs_spmm_plan* plan, const trs_half* B, void* C, int F, int out_dtype,
+                         int flags, void* workspace, size_t workspace_bytes, void* stream,
+                         int window_begin, int window_end);
+int trs_spmm_num_windows(const trs_spmm_plan* plan);
 /* Number of kernels one trs_spmm_run launches (1, or 2 when some window is split). */
 int trs_spmm_launches(const trs_spmm_plan* plan);
 
@@ -160,8 +167,21 @@ int trs_resident_create(const trs_format* host_format, int mOri, int kOri, int w
  * arrays stay caller-owned and must outlive the handle. */
 int trs_resident_create_device(const trs_format* dev_format, int mOri, int kOri, int window,
                                int max_dimN, trs_resident** out);
+/* One call, complete on return.  The result rows travel back to the host in window chunks while
+ * later chunks are still being computed.  timing (optional): h2d_ms, total_ms (kernels) and
+ * d2h_ms (first to last output copy; overlaps total_ms). */
 int trs_resident_forward(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN,
                          int out_dtype, trs_timing* timing);
+/* The same call without the wait, for a stream of SpMMs over one matrix (the reference's callers
+ * loop over spmm_forward_fp16_tcu_cuda_sptc_mma_parallel_online, mGCN_online.cpp:760, with a
+ * host->device and a device->host copy in every call; no asynchronous form exists there).  The
+ * handle keeps two device slots and three streams, so the input copy of call i+1 overlaps the
+ * kernels and the output copy of call i.  rhs_host / out_host must stay valid, and out_host
+ * unread, until trs_resident_wait returns; pinned host memory is needed for the overlap.
+ * trs_resident_wait blocks until every submitted call is complete and returns the first error. */
+int trs_resident_submit(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN,
+                        int out_dtype);
+int trs_resident_wait(trs_resident* h);
 int trs_resident_destroy(trs_resident* h);
 
 /* ---- un-packed SPTC arrays -> SpMM (compat) -------------------------------------------------

@@ -267,3 +267,60 @@ def test_bcast_epilogue_single_gpu():
     for b in bufs:
         assert torch.equal(b[row0:row0 + n], want)
         assert float(b[:row0].max()) == -7.0 and float(b[row0 + n:].min()) == -7.0
+
+
+def test_window_range_runs_cover_the_full_run(monkeypatch):
+    """trs_spmm_run_windows: disjoint window ranges write exactly their own rows and together
+    reproduce the full run bit for bit, also when windows are split into several work items."""
+    monkeypatch.setenv("TRS_CHUNK_STEPS", "8")  # many split windows -> the partial-sum path is cut too
+    rp, col, val = graphs.rmat_graph(11, 16, seed=9)
+    n = rp.numel() - 1
+    arrays, _ = O.build_format(rp, col, val)
+    B = torch.randn(n, 128, generator=torch.Generator().manual_seed(4)).half().cuda()
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    assert plan.launches >= 2
+    W = plan.num_windows
+    assert W == (n + 15) // 16
+    for dtype in (torch.float32, torch.float16):
+        want = plan.run(B, out_dtype=dtype)
+        out = torch.full((n, 128), -3.0, dtype=dtype, device="cuda")
+        cuts = [0, 1, W // 3, W // 3, W - 5, W]
+        for w0, w1 in zip(cuts[:-1], cuts[1:]):
+            before = out.clone()
+            plan.run_windows(B, out, w0, w1)
+            torch.cuda.synchronize()
+            changed = (out != before).any(dim=1).nonzero().flatten()
+            if changed.numel():
+                assert int(changed.min()) >= w0 * 16 and int(changed.max()) < w1 * 16
+        assert torch.equal(out, want)
+    from trspmm._lib import TrsError
+    with pytest.raises(TrsError):
+        plan.run_windows(B, out, 5, W + 1)
+    with pytest.raises(TrsError):
+        plan.run_windows(B, out, 7, 3)
+
+
+def test_resident_submit_wait_matches_blocking_calls(monkeypatch):
+    """A stream of trs_resident_submit calls (two device slots, three streams, output copied back
+    in window chunks) returns, for every call, the bits of the blocking trs_resident_forward."""
+    from trspmm import ResidentSpmm
+    monkeypatch.setenv("TRS_RESIDENT_CHUNKS", "5")
+    arrays, n = _golden("rmat_s9_minnnz")
+    fmt = Format(arrays)
+    res = ResidentSpmm(fmt, n, n, 16, 128)
+    g = torch.Generator().manual_seed(8)
+    Bs = [torch.randn(n, F, generator=g).half().pin_memory() for F in (128, 64, 128, 128, 32, 128)]
+    want = []
+    for b in Bs:
+        out = torch.empty((n, b.shape[1]), dtype=torch.float32).pin_memory()
+        res.forward(b, out)
+        want.append(out.clone())
+        assert O.scaled_max_error(out, O.spmm_from_format(arrays, b, n)) <= MAX_ERR_F32
+    for dtype in (torch.float32, torch.float16):
+        outs = [torch.full((n, b.shape[1]), float("nan"), dtype=dtype).pin_memory() for b in Bs]
+        for b, o in zip(Bs, outs):
+            res.submit(b, o)
+        res.wait()
+        for o, w in zip(outs, want):
+            assert torch.equal(o, w.to(dtype))
+    res.close()

@@ -149,17 +149,137 @@ struct EventPair {
 
 }  // namespace
 
+// Host-buffer handle.  Three streams (host->device, kernels, device->host) and two buffer slots
+// let consecutive calls overlap: the input copy of call i+1 runs beside the kernels and the
+// output copy of call i (PCIe is full duplex), and inside one call the result rows of a window
+// chunk go back to the host while the next chunk is computed.
+constexpr int kSlots = 2;
+constexpr int kMaxChunks = 16;
+
+struct ResidentSlot {
+    trs_half* d_rhs = nullptr;
+    void* d_out = nullptr;
+    cudaEvent_t in_done = nullptr, k_done = nullptr, out_done = nullptr;
+    cudaEvent_t chunk_done[kMaxChunks] = {};
+};
+
 struct trs_resident {
     Upload up;
     trs_format dev;
     trs_spmm_plan* plan = nullptr;
-    trs_half* d_rhs = nullptr;
-    void* d_out = nullptr;
+    ResidentSlot slot[kSlots];
     void* d_ws = nullptr;
     size_t ws_bytes = 0;
-    int m_rows = 0, k_cols = 0, max_dim = 0;
-    cudaStream_t stream = nullptr;
+    int m_rows = 0, k_cols = 0, max_dim = 0, window = 0, num_windows = 0;
+    cudaStream_t stream = nullptr;  // kernels
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t t_ev[6] = {};       // timing of the synchronous call
+    unsigned long long seq = 0;     // calls submitted so far
+    int pending_rc = TRS_OK;        // first error of a submitted call, reported by wait
 };
+
+namespace {
+
+int slot_init(trs_resident* h, int i) {
+    ResidentSlot& s = h->slot[i];
+    if (s.d_rhs) return TRS_OK;
+    int rc = h->up.raw<trs_half>((size_t)h->k_cols * h->max_dim, &s.d_rhs);
+    if (!rc) rc = h->up.raw<unsigned char>((size_t)h->m_rows * h->max_dim * sizeof(float), (unsigned char**)&s.d_out);
+    if (rc) return rc;
+    TRS_CUDA(cudaEventCreateWithFlags(&s.in_done, cudaEventDisableTiming));
+    TRS_CUDA(cudaEventCreateWithFlags(&s.k_done, cudaEventDisableTiming));
+    TRS_CUDA(cudaEventCreateWithFlags(&s.out_done, cudaEventDisableTiming));
+    for (int c = 0; c < kMaxChunks; ++c) TRS_CUDA(cudaEventCreateWithFlags(&s.chunk_done[c], cudaEventDisableTiming));
+    return TRS_OK;
+}
+
+int resident_finish_create(trs_resident* h, int mOri, int kOri, int window, int max_dimN) {
+    h->m_rows = mOri; h->k_cols = kOri; h->max_dim = max_dimN; h->window = window;
+    int rc = trs_spmm_plan_create(&h->dev, mOri, kOri, window, 1, nullptr, &h->plan);
+    if (!rc) rc = trs_spmm_workspace_bytes(h->plan, max_dimN, &h->ws_bytes);
+    if (!rc) rc = h->up.raw<unsigned char>(h->ws_bytes, (unsigned char**)&h->d_ws);
+    if (!rc) rc = slot_init(h, 0);  // the second slot is allocated by the first overlapping submit
+    if (rc) return rc;
+    h->num_windows = trs_spmm_num_windows(h->plan);
+    TRS_CUDA(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+    TRS_CUDA(cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking));
+    TRS_CUDA(cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 6; ++i) TRS_CUDA(cudaEventCreate(&h->t_ev[i]));
+    return TRS_OK;
+}
+
+// How many window chunks one call's output copy is cut into: the copy of a chunk overlaps the
+// kernels of the next one, so chunks only pay when the output is large.
+int resident_chunks(const trs_resident* h, size_t out_bytes) {
+    static const int forced = [] { const char* v = getenv("TRS_RESIDENT_CHUNKS"); return v ? atoi(v) : 0; }();
+    int k = forced > 0 ? forced : (out_bytes >= ((size_t)32 << 20) ? 8 : 1);
+    if (k > kMaxChunks) k = kMaxChunks;
+    if (k > h->num_windows) k = h->num_windows > 0 ? h->num_windows : 1;
+    return k;
+}
+
+// Enqueue one call on the three streams; returns without waiting.  `timed` records the six
+// timing events of the synchronous entry.
+int resident_enqueue(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN, int out_dtype, bool timed) {
+    const int si = (int)(h->seq % kSlots);
+    int rc = slot_init(h, si);
+    if (rc) return rc;
+    ResidentSlot& s = h->slot[si];
+    const size_t elt = out_dtype == TRS_OUT_F16 ? 2 : 4;
+    const size_t row_bytes = (size_t)dimN * elt;
+    const size_t out_bytes = (size_t)h->m_rows * row_bytes;
+    // input: the slot's B buffer is free once the kernels of the call two back are done
+    TRS_CUDA(cudaStreamWaitEvent(h->s_in, s.k_done, 0));
+    if (timed) cudaEventRecord(h->t_ev[0], h->s_in);
+    TRS_CUDA(cudaMemcpyAsync(s.d_rhs, rhs_host, (size_t)h->k_cols * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->s_in));
+    if (timed) cudaEventRecord(h->t_ev[1], h->s_in);
+    TRS_CUDA(cudaEventRecord(s.in_done, h->s_in));
+    // kernels: need this call's B and the slot's C buffer drained by the call two back
+    TRS_CUDA(cudaStreamWaitEvent(h->stream, s.in_done, 0));
+    TRS_CUDA(cudaStreamWaitEvent(h->stream, s.out_done, 0));
+    if (timed) cudaEventRecord(h->t_ev[2], h->stream);
+    const int chunks = resident_chunks(h, out_bytes);
+    for (int c = 0; c < chunks; ++c) {
+        const int w0 = (int)((long long)h->num_windows * c / chunks);
+        const int w1 = (int)((long long)h->num_windows * (c + 1) / chunks);
+        if (w1 <= w0) continue;
+        rc = trs_spmm_run_windows(h->plan, s.d_rhs, s.d_out, dimN, out_dtype, 0, h->d_ws, h->ws_bytes, h->stream, w0, w1);
+        if (rc) return rc;
+        TRS_CUDA(cudaEventRecord(s.chunk_done[c], h->stream));
+        TRS_CUDA(cudaStreamWaitEvent(h->s_out, s.chunk_done[c], 0));
+        if (timed && c == 0) cudaEventRecord(h->t_ev[4], h->s_out);
+        const size_t r0 = (size_t)w0 * h->window;
+        size_t r1 = (size_t)w1 * h->window;
+        if (r1 > (size_t)h->m_rows) r1 = (size_t)h->m_rows;
+        if (r1 > r0)
+            TRS_CUDA(cudaMemcpyAsync((char*)out_host + r0 * row_bytes, (const char*)s.d_out + r0 * row_bytes,
+                                     (r1 - r0) * row_bytes, cudaMemcpyDeviceToHost, h->s_out));
+    }
+    if (timed) cudaEventRecord(h->t_ev[3], h->stream);
+    TRS_CUDA(cudaEventRecord(s.k_done, h->stream));
+    if (timed) cudaEventRecord(h->t_ev[5], h->s_out);
+    TRS_CUDA(cudaEventRecord(s.out_done, h->s_out));
+    ++h->seq;
+    return TRS_OK;
+}
+
+int resident_drain(trs_resident* h) {
+    cudaError_t e1 = cudaStreamSynchronize(h->s_in);
+    cudaError_t e2 = cudaStreamSynchronize(h->stream);
+    cudaError_t e3 = cudaStreamSynchronize(h->s_out);
+    if (e1 != cudaSuccess) return (int)e1;
+    if (e2 != cudaSuccess) return (int)e2;
+    if (e3 != cudaSuccess) return (int)e3;
+    return TRS_OK;
+}
+
+int resident_check_args(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN, int out_dtype) {
+    if (!h || !rhs_host || !out_host || dimN <= 0 || dimN > h->max_dim) return TRS_E_ARG;
+    if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
+    return TRS_OK;
+}
+
+}  // namespace
 
 extern "C" int trs_resident_create(const trs_format* host_format, int mOri, int kOri, int window, int max_dimN,
                                    trs_resident** out) {
@@ -170,17 +290,8 @@ extern "C" int trs_resident_create(const trs_format* host_format, int mOri, int 
     if (trs_device_count() == 0) return TRS_E_NO_DEVICE;
     trs_resident* h = new trs_resident();
     int rc = upload_format(*host_format, h->up, &h->dev);
-    if (!rc) rc = trs_spmm_plan_create(&h->dev, mOri, kOri, window, 1, nullptr, &h->plan);
-    if (!rc) rc = trs_spmm_workspace_bytes(h->plan, max_dimN, &h->ws_bytes);
-    if (!rc) rc = h->up.raw<unsigned char>(h->ws_bytes, (unsigned char**)&h->d_ws);
-    if (!rc) rc = h->up.raw<trs_half>((size_t)kOri * max_dimN, &h->d_rhs);
-    if (!rc) rc = h->up.raw<unsigned char>((size_t)mOri * max_dimN * sizeof(float), (unsigned char**)&h->d_out);
-    if (!rc) {
-        cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
-        if (e != cudaSuccess) rc = (int)e;
-    }
+    if (!rc) rc = resident_finish_create(h, mOri, kOri, window, max_dimN);
     if (rc) { trs_resident_destroy(h); return rc; }
-    h->m_rows = mOri; h->k_cols = kOri; h->max_dim = max_dimN;
     *out = h;
     return TRS_OK;
 }
@@ -194,55 +305,66 @@ extern "C" int trs_resident_create_device(const trs_format* dev_format, int mOri
     if (trs_device_count() == 0) return TRS_E_NO_DEVICE;
     trs_resident* h = new trs_resident();
     h->dev = *dev_format;
-    int rc = trs_spmm_plan_create(&h->dev, mOri, kOri, window, 1, nullptr, &h->plan);
-    if (!rc) rc = trs_spmm_workspace_bytes(h->plan, max_dimN, &h->ws_bytes);
-    if (!rc) rc = h->up.raw<unsigned char>(h->ws_bytes, (unsigned char**)&h->d_ws);
-    if (!rc) rc = h->up.raw<trs_half>((size_t)kOri * max_dimN, &h->d_rhs);
-    if (!rc) rc = h->up.raw<unsigned char>((size_t)mOri * max_dimN * sizeof(float), (unsigned char**)&h->d_out);
-    if (!rc) {
-        cudaError_t e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
-        if (e != cudaSuccess) rc = (int)e;
-    }
+    int rc = resident_finish_create(h, mOri, kOri, window, max_dimN);
     if (rc) { trs_resident_destroy(h); return rc; }
-    h->m_rows = mOri; h->k_cols = kOri; h->max_dim = max_dimN;
     *out = h;
     return TRS_OK;
 }
 
 extern "C" int trs_resident_destroy(trs_resident* h) {
     if (!h) return TRS_OK;
+    if (h->stream) resident_drain(h);
     if (h->plan) trs_spmm_plan_destroy(h->plan);
+    for (int i = 0; i < kSlots; ++i) {
+        ResidentSlot& s = h->slot[i];
+        if (s.in_done) cudaEventDestroy(s.in_done);
+        if (s.k_done) cudaEventDestroy(s.k_done);
+        if (s.out_done) cudaEventDestroy(s.out_done);
+        for (int c = 0; c < kMaxChunks; ++c)
+            if (s.chunk_done[c]) cudaEventDestroy(s.chunk_done[c]);
+    }
+    for (int i = 0; i < 6; ++i)
+        if (h->t_ev[i]) cudaEventDestroy(h->t_ev[i]);
     if (h->stream) cudaStreamDestroy(h->stream);
+    if (h->s_in) cudaStreamDestroy(h->s_in);
+    if (h->s_out) cudaStreamDestroy(h->s_out);
     delete h;
     return TRS_OK;
 }
 
 extern "C" int trs_resident_forward(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN, int out_dtype,
                                     trs_timing* timing) {
-    if (!h || !rhs_host || !out_host || dimN <= 0 || dimN > h->max_dim) return TRS_E_ARG;
-    if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
-    const size_t out_bytes = (size_t)h->m_rows * dimN * (out_dtype == TRS_OUT_F16 ? 2 : 4);
-    EventPair ev_in, ev_k, ev_out;
-    if (timing) {
-        memset(timing, 0, sizeof(*timing));
-        int rc = ev_in.init(); if (!rc) rc = ev_k.init(); if (!rc) rc = ev_out.init();
-        if (rc) return rc;
-        cudaEventRecord(ev_in.a, h->stream);
-    }
-    TRS_CUDA(cudaMemcpyAsync(h->d_rhs, rhs_host, (size_t)h->k_cols * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->stream));
-    if (timing) { cudaEventRecord(ev_in.b, h->stream); cudaEventRecord(ev_k.a, h->stream); }
-    int rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, out_dtype, h->d_ws, h->ws_bytes, h->stream);
+    int rc = resident_check_args(h, rhs_host, out_host, dimN, out_dtype);
     if (rc) return rc;
-    if (timing) { cudaEventRecord(ev_k.b, h->stream); cudaEventRecord(ev_out.a, h->stream); }
-    TRS_CUDA(cudaMemcpyAsync(out_host, h->d_out, out_bytes, cudaMemcpyDeviceToHost, h->stream));
-    if (timing) cudaEventRecord(ev_out.b, h->stream);
-    TRS_CUDA(cudaStreamSynchronize(h->stream));
+    if (timing) memset(timing, 0, sizeof(*timing));
+    rc = resident_enqueue(h, rhs_host, out_host, dimN, out_dtype, timing != nullptr);
+    const int drc = resident_drain(h);
+    if (!rc) rc = drc;
+    if (!rc && h->pending_rc) { rc = h->pending_rc; }
+    h->pending_rc = TRS_OK;
+    if (rc) return rc;
     if (timing) {
-        timing->h2d_ms = ev_in.ms();
-        timing->total_ms = ev_k.ms();
-        timing->d2h_ms = ev_out.ms();
+        cudaEventElapsedTime(&timing->h2d_ms, h->t_ev[0], h->t_ev[1]);
+        cudaEventElapsedTime(&timing->total_ms, h->t_ev[2], h->t_ev[3]);
+        cudaEventElapsedTime(&timing->d2h_ms, h->t_ev[4], h->t_ev[5]);
     }
     return TRS_OK;
+}
+
+extern "C" int trs_resident_submit(trs_resident* h, const trs_half* rhs_host, void* out_host, int dimN, int out_dtype) {
+    int rc = resident_check_args(h, rhs_host, out_host, dimN, out_dtype);
+    if (rc) return rc;
+    rc = resident_enqueue(h, rhs_host, out_host, dimN, out_dtype, false);
+    if (rc && !h->pending_rc) h->pending_rc = rc;
+    return rc;
+}
+
+extern "C" int trs_resident_wait(trs_resident* h) {
+    if (!h) return TRS_E_ARG;
+    int rc = resident_drain(h);
+    if (!rc) rc = h->pending_rc;
+    h->pending_rc = TRS_OK;
+    return rc;
 }
 
 extern "C" int trs_spmm_forward_host(const trs_format* host_format, const trs_half* rhs_host, float* out_host, int dimN,
@@ -258,20 +380,20 @@ extern "C" int trs_spmm_forward_host(const trs_format* host_format, const trs_ha
     EventPair ev;
     rc = ev.init();
     if (!rc) {
-        cudaError_t e = cudaMemcpyAsync(h->d_rhs, rhs_host, (size_t)kOri * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->stream);
+        cudaError_t e = cudaMemcpyAsync(h->slot[0].d_rhs, rhs_host, (size_t)kOri * dimN * sizeof(trs_half), cudaMemcpyHostToDevice, h->stream);
         if (e != cudaSuccess) rc = (int)e;
     }
     // one untimed run, then `epoches` timed ones (mGCNkernel_online.cu:1604-1687 warms up and
     // averages over epoches the same way); C is fully rewritten by every run
-    if (!rc) rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
+    if (!rc) rc = trs_spmm_run(h->plan, h->slot[0].d_rhs, h->slot[0].d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
     if (!rc) {
         cudaEventRecord(ev.a, h->stream);
         for (int i = 0; i < epoches && !rc; ++i)
-            rc = trs_spmm_run(h->plan, h->d_rhs, h->d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
+            rc = trs_spmm_run(h->plan, h->slot[0].d_rhs, h->slot[0].d_out, dimN, TRS_OUT_F32, h->d_ws, h->ws_bytes, h->stream);
         cudaEventRecord(ev.b, h->stream);
     }
     if (!rc) {
-        cudaError_t e = cudaMemcpyAsync(out_host, h->d_out, (size_t)mOri * dimN * sizeof(float), cudaMemcpyDeviceToHost, h->stream);
+        cudaError_t e = cudaMemcpyAsync(out_host, h->slot[0].d_out, (size_t)mOri * dimN * sizeof(float), cudaMemcpyDeviceToHost, h->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
         if (e != cudaSuccess) rc = (int)e;
     }

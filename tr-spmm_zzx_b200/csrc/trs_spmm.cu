@@ -1080,6 +1080,7 @@ struct trs_spmm_plan {
     DevBuf<__half> tc_dense;          // expanded TC blocks for the bulk-copy kernel
     DevBuf<unsigned char> zeros;      // 512 zero bytes + the status word behind them
     int n_items, n_heavy, n_slots;
+    std::vector<int> h_item_off, h_heavy_off;  // host copies of the per-window prefixes (num_windows + 1 each)
     bool bulk_ok;                     // bulk-copy kernel requested and usable
     bool arrays_aligned;              // index / tile arrays are 16-byte aligned
     // persistent flat-stream kernel
@@ -1284,6 +1285,13 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail((int)e);
     p->n_items = totals[0]; p->n_heavy = totals[1]; p->n_slots = totals[2];
+    // per-window prefixes on the host, so that a run can be restricted to a window range
+    p->h_item_off.resize((size_t)W + 1);
+    p->h_heavy_off.resize((size_t)W + 1);
+    e = cudaMemcpy(p->h_item_off.data(), off.p, sizeof(int) * ((size_t)W + 1), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess)
+        e = cudaMemcpy(p->h_heavy_off.data(), off.p + (W + 1), sizeof(int) * ((size_t)W + 1), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail((int)e);
     rc = p->items.alloc(p->n_items);
     if (!rc) rc = p->heavy.alloc(p->n_heavy);
     if (rc) return fail(rc);
@@ -1426,12 +1434,22 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
 
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
                     size_t workspace_bytes, void* stream, bool items_only, void* const* peers = nullptr, int n_peers = 0,
-                    long long peer_row0 = 0);
+                    long long peer_row0 = 0, int w0 = 0, int w1 = -1);
 
 extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
                                void* workspace, size_t workspace_bytes, void* stream) {
     return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, false);
 }
+
+extern "C" int trs_spmm_run_windows(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
+                                    void* workspace, size_t workspace_bytes, void* stream, int window_begin,
+                                    int window_end) {
+    if (window_end < 0) return TRS_E_ARG;
+    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, /*items_only=*/true, nullptr, 0, 0,
+                    window_begin, window_end);
+}
+
+extern "C" int trs_spmm_num_windows(const trs_spmm_plan* p) { return p ? p->num_windows : TRS_E_ARG; }
 
 extern "C" int trs_spmm_run_bcast(const trs_spmm_plan* p, const trs_half* B, void* const* dst, int n_dst, long long row0,
                                   int F, int flags, void* workspace, size_t workspace_bytes, void* stream) {
@@ -1444,17 +1462,23 @@ extern "C" int trs_spmm_run_bcast(const trs_spmm_plan* p, const trs_half* B, voi
 
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
                     size_t workspace_bytes, void* stream, bool items_only, void* const* peers, int n_peers,
-                    long long peer_row0) {
+                    long long peer_row0, int w0, int w1) {
     if (!p || !B || !C || F <= 0) return TRS_E_ARG;
+    if (w1 < 0) w1 = p->num_windows;
+    if (w0 < 0 || w0 > w1 || w1 > p->num_windows) return TRS_E_ARG;
+    if (w0 == w1) return TRS_OK;
+    // window range -> item / split-window ranges (both lists are in window order)
+    const int i0 = p->h_item_off[w0], n_items = p->h_item_off[w1] - i0;
+    const int h0 = p->h_heavy_off[w0], n_heavy = p->h_heavy_off[w1] - h0;
     if (flags & ~TRS_EPILOGUE_RELU) return TRS_E_ARG;
     if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
-    const bool flat = !items_only && flat_usable(p, F) && (((uintptr_t)B & 15) == 0);
+    const bool flat = !items_only && w0 == 0 && w1 == p->num_windows && flat_usable(p, F) && (((uintptr_t)B & 15) == 0);
     size_t need = flat ? flat_scratch_bytes(p, F) : items_scratch_bytes(p, F);
     if (flat && p->flat_G <= 1) need = 0;
     if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     KernelArgs a;
-    a.f = p->f; a.wr = p->wr; a.items = p->items.p;
+    a.f = p->f; a.wr = p->wr; a.items = p->items.p + i0;
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
     a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
@@ -1469,18 +1493,18 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     }
     const bool bulk = p->bulk_ok && n_peers == 0 && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
     if (bulk) {
-        if (F <= 32) rc = launch_bulk_kernel<1>(a, p->n_items, st);
-        else if (F <= 64) rc = launch_bulk_kernel<2>(a, p->n_items, st);
-        else rc = launch_bulk_kernel<4>(a, p->n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
-    } else if (F <= 32) rc = launch_window_kernel<1>(a, p->n_items, p->arrays_aligned, st);
-    else if (F <= 64) rc = launch_window_kernel<2>(a, p->n_items, p->arrays_aligned, st);
-    else rc = launch_window_kernel<4>(a, p->n_items, p->arrays_aligned, st);
+        if (F <= 32) rc = launch_bulk_kernel<1>(a, n_items, st);
+        else if (F <= 64) rc = launch_bulk_kernel<2>(a, n_items, st);
+        else rc = launch_bulk_kernel<4>(a, n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
+    } else if (F <= 32) rc = launch_window_kernel<1>(a, n_items, p->arrays_aligned, st);
+    else if (F <= 64) rc = launch_window_kernel<2>(a, n_items, p->arrays_aligned, st);
+    else rc = launch_window_kernel<4>(a, n_items, p->arrays_aligned, st);
     if (rc) return rc;
-    if (p->n_heavy > 0) {
+    if (n_heavy > 0) {
         PeerDst pd;
         pd.n = a.n_peers; pd.row0 = a.peer_row0;
         for (int d = 0; d < 8; ++d) pd.ptr[d] = a.peers[d];
-        k_reduce_heavy<<<p->n_heavy, 256, 0, st>>>(p->heavy.p, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half, a.relu, pd);
+        k_reduce_heavy<<<n_heavy, 256, 0, st>>>(p->heavy.p + h0, (const float*)workspace, C, F, p->m_rows, p->window, a.out_half, a.relu, pd);
         TRS_LAUNCH_CHECK();
     }
     return TRS_OK;

@@ -89,6 +89,14 @@ def load():
     lib.trs_resident_create_device.restype = i32
     lib.trs_resident_forward.argtypes = [vp, vp, vp, i32, i32, C.POINTER(TrsTiming)]
     lib.trs_resident_destroy.argtypes = [vp]
+    lib.trs_resident_submit.argtypes = [vp, vp, vp, i32, i32]
+    lib.trs_resident_submit.restype = i32
+    lib.trs_resident_wait.argtypes = [vp]
+    lib.trs_resident_wait.restype = i32
+    lib.trs_spmm_run_windows.argtypes = [vp, vp, vp, i32, i32, i32, vp, sz, vp, i32, i32]
+    lib.trs_spmm_run_windows.restype = i32
+    lib.trs_spmm_num_windows.argtypes = [vp]
+    lib.trs_spmm_num_windows.restype = i32
     lib.trs_sptc_unpacked_forward_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32,
                                                    C.POINTER(TrsTiming)]
     lib.trs_sddmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]

@@ -82,6 +82,30 @@ class SpmmPlan:
                                                 _lib.current_stream_ptr(self.device)))
         return out
 
+    @property
+    def num_windows(self) -> int:
+        return self.lib.trs_spmm_num_windows(self._handle)
+
+    def run_windows(self, B: torch.Tensor, out: torch.Tensor, window_begin: int, window_end: int,
+                    relu: bool = False) -> torch.Tensor:
+        """trs_spmm_run_windows: the product restricted to the row windows [window_begin, window_end);
+        only those rows of `out` are written."""
+        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
+            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
+        F = B.shape[1]
+        if out.shape != (self.m_rows, F) or not out.is_contiguous() or out.device != self.device:
+            raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
+        ws = self._ws.get(F)
+        if ws is None:
+            ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
+            self._ws[F] = ws
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.trs_spmm_run_windows(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
+                                                     1 if relu else 0, ws.data_ptr(), ws.numel(),
+                                                     _lib.current_stream_ptr(self.device), int(window_begin),
+                                                     int(window_end)))
+        return out
+
     def run_bcast(self, B: torch.Tensor, dst_ptrs, row0: int, relu: bool = False):
         """trs_spmm_run_bcast: the fp16 result rows go straight from the kernel's epilogue into every
         buffer of `dst_ptrs` (device pointers of [N_total, F] fp16 matrices: this GPU's and its
@@ -156,6 +180,7 @@ class ResidentSpmm:
         self.lib = _lib.load()
         self._handle = C.c_void_p()
         self.mOri, self.kOri, self.max_dimN = mOri, kOri, max_dimN
+        self._inflight = []  # host tensors of submitted calls, kept alive until wait()
         if fmt.device.type == "cuda":  # e.g. straight from the GPU builder: no host round trip
             self._keep = fmt.half_values().contiguous()
             cf = self._keep.c_struct()
@@ -174,6 +199,27 @@ class ResidentSpmm:
         _lib.check(self.lib.trs_resident_forward(self._handle, rhs.data_ptr(), out.data_ptr(), rhs.shape[1],
                                                  _out_code(out.dtype), C.byref(timing)))
         return out, timing
+
+    def submit(self, rhs: torch.Tensor, out: torch.Tensor):
+        """trs_resident_submit: enqueue one call and return at once.  Consecutive submits overlap
+        (input copy of the next call beside the kernels and the output copy of this one); `rhs`
+        and `out` must be pinned host tensors that stay untouched until wait() returns."""
+        if rhs.device.type != "cpu" or out.device.type != "cpu":
+            raise ValueError("ResidentSpmm.submit takes host tensors")
+        if not rhs.is_contiguous() or not out.is_contiguous() or rhs.dtype != torch.float16:
+            raise ValueError("rhs must be contiguous fp16, out contiguous")
+        if rhs.shape[0] != self.kOri or out.shape != (self.mOri, rhs.shape[1]):
+            raise ValueError("shape mismatch")
+        self._inflight.append((rhs, out))
+        _lib.check(self.lib.trs_resident_submit(self._handle, rhs.data_ptr(), out.data_ptr(), rhs.shape[1],
+                                                _out_code(out.dtype)))
+
+    def wait(self):
+        """trs_resident_wait: block until every submitted call is complete."""
+        try:
+            _lib.check(self.lib.trs_resident_wait(self._handle))
+        finally:
+            self._inflight.clear()
 
     def close(self):
         if self._handle:
