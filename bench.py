@@ -225,6 +225,16 @@ def run_ours(args, rank, world, local_rank):
     rp, col, val, F = make_matrix(args.workload, dev)
     n = rp.numel() - 1
     nnz_total = col.numel()
+    reorder_note = None
+    if args.reorder != "none":
+        # labelled configuration: rows re-ordered (columns keep their ids), C comes out in the new row order
+        from trspmm import reorder as R
+        before = R.window_column_pairs(rp, col)
+        rid = R.row_order(rp, col, args.reorder, n_cols=n)
+        rp, col, val = R.permute_rows(rp, col, val, rid)
+        reorder_note = {"method": args.reorder, "window_column_pairs_before": before,
+                        "window_column_pairs_after": R.window_column_pairs(rp, col)}
+        del rid
     if world > 1:
         # first cut by nnz; then re-cut by the k-steps the built format really has per window
         # (hub windows share columns, so their cost per nnz is lower) and build again
@@ -322,7 +332,8 @@ def run_ours(args, rank, world, local_rank):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": args.workload, "description": DESCRIPTIONS[args.workload], "n_rows": n,
+            "config": {"workload": args.workload + ("" if reorder_note is None else "+rows:" + args.reorder),
+                       "reorder": reorder_note, "description": DESCRIPTIONS[args.workload], "n_rows": n,
                        "nnz": nnz_total, "kept_nnz": int(kept_total), "F": F, "out": "f16",
                        "parallelism": f"row-window shards x{world} balanced by k-steps, B replicated, no collective",
                        "l2": "inputs larger than L2 (no flush)" if n * F * 2 > 126e6 else "B fits L2",
@@ -330,7 +341,7 @@ def run_ours(args, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "algorithmic_bytes_per_step_rank0": alg_rank,
                          "algorithmic_bytes_per_step_job": alg_job,
-                         "traffic": MEASURED_TRAFFIC.get((args.workload, F)) if world == 1 else None,
+                         "traffic": MEASURED_TRAFFIC.get((args.workload, F)) if (world == 1 and reorder_note is None) else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch (profiles/)",
                          "kernel": "k_window_spmm_lean"},
             "e2e": {"value": 2.0 * kept_total * F / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
@@ -459,6 +470,8 @@ def main():
     ap.add_argument("--workload", default="rmat21", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--reorder", default="none", choices=["none", "minhash", "hub", "degree"],
+                    help="spmm: re-order the rows first (a separate, labelled configuration)")
     ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
     ap.add_argument("--gather", default="h1", choices=["h1", "z2", "fused"], help="gcn: which matrix the ranks exchange")

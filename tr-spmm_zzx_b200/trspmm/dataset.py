@@ -83,6 +83,15 @@ class GCN_dataset_tcu_sptc_cuda_online(torch.nn.Module):
         src = torch.as_tensor(np.asarray(graph["src_li"]), device=dev)
         dst = torch.as_tensor(np.asarray(graph["dst_li"]), device=dev)
         self.row_pointers, self.column_index = edges_to_csr(src, dst, self.num_nodes_ori, self.num_nodes_dst, window)
+        # row reordering slot of the reference (mdataset2_online.py:73-94, LIBRA_TCA_REORDER=1):
+        # rows move, columns keep their ids; reorder_id maps new row -> old row
+        self.reorder_id = None
+        if os.environ.get("LIBRA_TCA_REORDER", "0") == "1":
+            from .reorder import permute_rows, row_order
+            self.reorder_id = row_order(self.row_pointers, self.column_index,
+                                        os.environ.get("TRS_REORDER_METHOD", "minhash"), n_cols=self.num_nodes_dst)
+            self.row_pointers, self.column_index, _ = permute_rows(self.row_pointers, self.column_index, None,
+                                                                   self.reorder_id)
         self.num_edges = self.column_index.numel()
         gen = torch.Generator(device=dev)
         if seed is not None:
