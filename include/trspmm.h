@@ -268,6 +268,21 @@ int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, in
  * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e. */
 int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y,
               trs_half* out, int n_rows, int n_cols, int K, void* stream);
+/* Planned SDDMM for a pattern that is used many times (training epochs): the plan groups the
+ * entries by (16-row window, column), so that each distinct Y row of a window is gathered once
+ * and the dot products run on the tensor cores (mma m16n8k16, fp32 accumulate) for K = 32, 64,
+ * 128 with 16-byte aligned X / Y; other shapes run the entry-parallel kernel of trs_sddmm.  The
+ * pattern must be canonical CSR (columns ascending and unique inside a row) and stay valid and
+ * unchanged while the plan lives.  Results equal trs_sddmm's up to fp32 summation order.
+ * No counterpart in the reference. */
+typedef struct trs_sddmm_plan trs_sddmm_plan;
+int trs_sddmm_plan_create(const int32_t* rowptr, const int32_t* col, int n_rows, int n_cols,
+                          void* stream, trs_sddmm_plan** out);
+int trs_sddmm_plan_run(const trs_sddmm_plan* plan, const trs_half* X, const trs_half* Y,
+                       trs_half* out, int K, void* stream);
+/* distinct (window, column) pairs and 8-column blocks of the plan */
+int trs_sddmm_plan_info(const trs_sddmm_plan* plan, long long* n_pairs, long long* n_blocks);
+int trs_sddmm_plan_destroy(trs_sddmm_plan* plan);
 
 #ifdef __cplusplus
 }

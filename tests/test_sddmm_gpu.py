@@ -43,3 +43,56 @@ def test_sddmm_rectangular_and_empty_rows():
     rp0 = torch.zeros(301, dtype=torch.int32).cuda()
     out0 = sddmm(rp0, torch.zeros(0, dtype=torch.int32).cuda(), X.cuda(), Y.cuda())
     assert out0.numel() == 0
+
+
+@pytest.mark.parametrize("K", [64, 32, 128, 24])
+@pytest.mark.parametrize("gen", ["uniform", "rmat", "clustered"])
+def test_planned_sddmm_matches_oracle_and_the_unplanned_entry(gen, K):
+    """trs_sddmm_plan_*: tensor-core path for K in {32, 64, 128}, fallback otherwise; every entry
+    must be written (the output starts as NaN) and agree with the CPU definition."""
+    from trspmm import SddmmPlan
+    if gen == "uniform":
+        rp, col, _ = graphs.uniform_graph(1000, 9, seed=1)        # 1000 rows: ragged last window
+    elif gen == "rmat":
+        rp, col, _ = graphs.rmat_graph(11, 12, seed=1)            # hub windows: hundreds of blocks
+    else:
+        rp, col, _ = graphs.clustered_graph(2048, community=64, intra=12, glob=2, seed=2)
+    n = rp.numel() - 1
+    g = torch.Generator().manual_seed(K)
+    X = torch.randn(n, K, generator=g).half()
+    Y = torch.randn(n, K, generator=g).half()
+    ref = O.sddmm_csr(rp, col, X, Y)
+    plan = SddmmPlan(rp.cuda(), col.cuda(), n)
+    assert 0 < plan.n_pairs <= col.numel() and plan.n_blocks * 8 >= plan.n_pairs
+    out = torch.full((col.numel(),), float("nan"), dtype=torch.float16, device="cuda")
+    plan.run(X.cuda(), Y.cuda(), out=out)
+    out = out.cpu()
+    assert not torch.isnan(out).any()
+    mx, mean = O.rel_errors(out, ref)
+    assert mx <= 1e-2 and mean <= 1e-3
+    again = plan.run(X.cuda(), Y.cuda()).cpu()
+    assert torch.equal(again, out)                                # deterministic
+    plain = sddmm(rp.cuda(), col.cuda(), X.cuda(), Y.cuda()).cpu()
+    assert O.rel_errors(out, plain.float())[0] <= 1e-2
+
+
+def test_planned_sddmm_rectangular_empty_rows_and_empty_pattern():
+    from trspmm import SddmmPlan
+    g = torch.Generator().manual_seed(0)
+    rows = torch.randint(0, 300, (2000,), generator=g)
+    rows[rows % 7 == 0] = 1
+    cols = torch.randint(0, 500, (2000,), generator=g)
+    rp, col, _ = graphs.coo_to_csr(rows, cols, 300, 500)
+    X = torch.randn(300, 64, generator=g).half()
+    Y = torch.randn(500, 64, generator=g).half()
+    ref = O.sddmm_csr(rp, col, X, Y)
+    plan = SddmmPlan(rp.cuda(), col.cuda(), 500)
+    out = torch.full((col.numel(),), float("nan"), dtype=torch.float16, device="cuda")
+    plan.run(X.cuda(), Y.cuda(), out=out)
+    assert not torch.isnan(out).any()
+    assert O.rel_errors(out.cpu(), ref)[0] <= 1e-2
+    # the number of pairs is the number of distinct (window, column) keys
+    r = torch.repeat_interleave(torch.arange(300), (rp[1:] - rp[:-1]).long())
+    assert plan.n_pairs == torch.unique((r // 16) * 500 + col.long()).numel()
+    empty = SddmmPlan(torch.zeros(301, dtype=torch.int32).cuda(), torch.zeros(0, dtype=torch.int32).cuda(), 500)
+    assert empty.n_blocks == 0 and empty.run(X.cuda(), Y.cuda()).numel() == 0

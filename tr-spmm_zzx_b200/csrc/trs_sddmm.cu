@@ -8,6 +8,8 @@
 // slices of X[row] and Y[col] with one 16-byte load per lane, multiplies in fp32 and reduces
 // with three shuffles.  The row of an entry is found once per warp by binary search in the row
 // pointers and then advanced linearly.
+#include <cub/cub.cuh>
+
 #include "trs_common.cuh"
 
 namespace trs {
@@ -108,7 +110,316 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
     }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Planned, tensor-core SDDMM
+// ----------------------------------------------------------------------------------------------
+// The entry-parallel kernel above gathers one Y row per ENTRY and spends ~19 warp instructions
+// per entry on conversions, FMAs and shuffles.  With a plan over the pattern the work is done per
+// (16-row window, column) PAIR instead: the distinct columns of a window, ascending, are cut into
+// blocks of 8; for a block one warp multiplies the window's X tile (16 x K) with the 8 gathered
+// Y rows on the tensor cores (mma m16n8k16, fp32 accumulate) and stores only the dot products
+// the pattern has.  The contraction runs over the feature dimension, which is contiguous in
+// both operands, so the fragments are filled by plain 16-byte loads: lane (g, t) reads bytes
+// [64 c + 16 t, +16) of X[row g], X[row g + 8] and Y[col g] for every 32-feature chunk c — the
+// same feature positions on both sides, which is all the MMA needs (the order of the k index
+// inside a chunk is free).
+//
+// Block record (128 bytes, one cache line): 8 column ids (-1 = unused slot), a 16 x 8 bitmap of
+// the entries present (bit 8 r + n), the window id, and for each of the 16 rows the CSR index of
+// its first entry inside the block.  Columns ascend inside a CSR row and a block holds a
+// contiguous run of the window's sorted distinct columns, so the entries of a row inside a block
+// are consecutive in CSR order: entry (r, n) = start[r] + popcount(rowbits(r) below bit n).
+// The pattern must be canonical CSR (columns ascending and unique per row).
+struct SddmmBlock {
+    int col[8];
+    unsigned bits[4];
+    int window;
+    int pad[3];
+    int start[16];
+};
+static_assert(sizeof(SddmmBlock) == 128, "one cache line per block");
+
+__device__ __forceinline__ int row_of_entry(const int* __restrict__ rowptr, int n_rows, long long e) {
+    int lo = 0, hi = n_rows;  // largest r with rowptr[r] <= e
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long)rowptr[mid] <= e) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void ksp_keys(const int* __restrict__ rowptr, const int* __restrict__ col, int n_rows, long long nnz,
+                         unsigned long long* __restrict__ key, int* __restrict__ ent) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= nnz) return;
+    const int r = row_of_entry(rowptr, n_rows, e);
+    key[e] = ((unsigned long long)(r >> 4) << 32) | (unsigned)col[e];
+    ent[e] = (int)e;
+}
+
+__global__ void ksp_heads(const unsigned long long* __restrict__ key, long long nnz, int* __restrict__ head) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    head[i] = (i == 0 || key[i] != key[i - 1]) ? 1 : 0;
+}
+
+// first_pair[w] = number of distinct (window, column) pairs in windows < w, for w in [0, W]
+__global__ void ksp_window_pairs(const unsigned long long* __restrict__ key, const int* __restrict__ pair_idx,
+                                 long long nnz, int total_pairs, int W, int* __restrict__ first_pair,
+                                 int* __restrict__ blocks_of) {
+    const int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w > W) return;
+    auto lower = [&](int win) -> int {  // pairs before the first sorted entry of window >= win
+        long long lo = 0, hi = nnz;     // first i with key[i] >> 32 >= win
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if ((int)(key[mid] >> 32) < win) lo = mid + 1; else hi = mid;
+        }
+        return lo < nnz ? pair_idx[lo] : total_pairs;
+    };
+    const int mine = lower(w);
+    first_pair[w] = mine;
+    if (w < W) blocks_of[w] = (lower(w + 1) - mine + 7) >> 3;
+}
+
+__global__ void ksp_init_blocks(SddmmBlock* __restrict__ blk, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one int of a record per thread
+    if (i >= n * 32) return;
+    const int f = (int)(i & 31);
+    int v = 0;
+    if (f < 8) v = -1;
+    else if (f >= 16) v = 0x7fffffff;
+    ((int*)blk)[i] = v;
+}
+
+__global__ void ksp_fill(const unsigned long long* __restrict__ key, const int* __restrict__ ent,
+                         const int* __restrict__ pair_idx, const int* __restrict__ head,
+                         const int* __restrict__ first_pair, const int* __restrict__ blk_off,
+                         const int* __restrict__ rowptr, int n_rows, long long nnz, SddmmBlock* __restrict__ blk) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    const unsigned long long k = key[i];
+    const int w = (int)(k >> 32);
+    const int local = pair_idx[i] - first_pair[w];
+    SddmmBlock* b = blk + (size_t)blk_off[w] + (local >> 3);
+    const int n = local & 7;
+    const int e = ent[i];
+    const int r = row_of_entry(rowptr, n_rows, e) - (w << 4);
+    atomicOr(&b->bits[r >> 2], 1u << (((r & 3) << 3) + n));
+    atomicMin(&b->start[r], e);
+    if (head[i]) {
+        b->col[n] = (int)(unsigned)k;
+        if (n == 0) b->window = w;
+    }
+}
+
+constexpr int kSddmmBlocksPerWarp = 16;
+constexpr int kSddmmUnroll = 4;
+
+template <int KCH>  // K = 32 * KCH
+__global__ void __launch_bounds__(128) k_sddmm_tc(const SddmmBlock* __restrict__ blk, long long n_blocks,
+                                                  const __half* __restrict__ X, const __half* __restrict__ Y,
+                                                  __half* __restrict__ out, int n_rows) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long b0 = warp * kSddmmBlocksPerWarp;
+    if (b0 >= n_blocks) return;
+    const long long b1 = min(b0 + (long long)kSddmmBlocksPerWarp, n_blocks);
+    constexpr int ROW16 = KCH * 4;  // 16-byte units per row
+    const uint4* Xq = (const uint4*)X;
+    const uint4* Yq = (const uint4*)Y;
+
+    int cur_w = -1;
+    uint4 xa[KCH], xb[KCH];  // X[row g], X[row g + 8]: this lane's 16 bytes of every chunk
+#pragma unroll
+    for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
+
+    for (long long bb = b0; bb < b1; bb += kSddmmUnroll) {
+        uint4 yv[kSddmmUnroll][KCH];
+#pragma unroll
+        for (int u = 0; u < kSddmmUnroll; ++u) {
+            if (bb + u < b1) {
+                const int c = max(__ldg(&blk[bb + u].col[g]), 0);  // unused slot: any valid row, result not stored
+#pragma unroll
+                for (int ch = 0; ch < KCH; ++ch) yv[u][ch] = __ldg(Yq + (size_t)c * ROW16 + ch * 4 + t);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kSddmmUnroll; ++u) {
+            if (bb + u >= b1) break;
+            const SddmmBlock* b = blk + bb + u;
+            const int w = __ldg(&b->window);
+            if (w != cur_w) {  // warp-uniform
+                cur_w = w;
+                const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
+#pragma unroll
+                for (int ch = 0; ch < KCH; ++ch) {
+                    xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4 + t);
+                    xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4 + t);
+                }
+            }
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ch = 0; ch < KCH; ++ch) {
+                mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, yv[u][ch].x, yv[u][ch].y);
+                mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, yv[u][ch].z, yv[u][ch].w);
+            }
+            // d[0], d[1]: row g, slots 2t, 2t+1;  d[2], d[3]: row g + 8
+            const unsigned wa = __ldg(&b->bits[g >> 2]), wb = __ldg(&b->bits[(g >> 2) + 2]);
+            const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
+            const int n0 = 2 * t;
+            if ((ba >> n0) & 3u) {
+                const int s = __ldg(&b->start[g]) + __popc(ba & ((1u << n0) - 1u));
+                if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
+                if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
+            }
+            if ((bbits >> n0) & 3u) {
+                const int s = __ldg(&b->start[g + 8]) + __popc(bbits & ((1u << n0) - 1u));
+                if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
+                if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
+            }
+        }
+    }
+}
+
 }  // namespace trs
+
+struct trs_sddmm_plan {
+    const int32_t* rowptr = nullptr;  // caller-owned pattern (used by the fallback kernel)
+    const int32_t* col = nullptr;
+    int n_rows = 0, n_cols = 0;
+    long long nnz = 0, n_blocks = 0, n_pairs = 0;
+    trs::DevBuf<trs::SddmmBlock> blocks;
+};
+
+extern "C" int trs_sddmm_plan_destroy(trs_sddmm_plan* p) {
+    if (!p) return TRS_OK;
+    p->blocks.release();
+    delete p;
+    return TRS_OK;
+}
+
+extern "C" int trs_sddmm_plan_create(const int32_t* rowptr, const int32_t* col, int n_rows, int n_cols, void* stream,
+                                     trs_sddmm_plan** out) {
+    using namespace trs;
+    if (!out) return TRS_E_ARG;
+    *out = nullptr;
+    if (!rowptr || n_rows <= 0 || n_cols <= 0) return TRS_E_ARG;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return TRS_E_NO_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    int ends[2] = {0, 0};
+    TRS_CUDA(cudaMemcpyAsync(&ends[0], rowptr, sizeof(int), cudaMemcpyDeviceToHost, st));
+    TRS_CUDA(cudaMemcpyAsync(&ends[1], rowptr + n_rows, sizeof(int), cudaMemcpyDeviceToHost, st));
+    TRS_CUDA(cudaStreamSynchronize(st));
+    if (ends[0] != 0 || ends[1] < 0) return TRS_E_OFFSETS;
+    const long long nnz = ends[1];
+    if (nnz > 0 && !col) return TRS_E_ARG;
+    trs_sddmm_plan* p = new trs_sddmm_plan();
+    p->rowptr = rowptr; p->col = col; p->n_rows = n_rows; p->n_cols = n_cols; p->nnz = nnz;
+    if (nnz == 0) { *out = p; return TRS_OK; }
+
+    const int W = (n_rows + 15) / 16;
+    DevBuf<unsigned long long> key_a, key_b;
+    DevBuf<int> ent_a, ent_b, head, pair_idx, first_pair, blocks_of, blk_off;
+    DevBuf<unsigned char> tmp;
+    auto cleanup = [&]() {
+        key_a.release(); key_b.release(); ent_a.release(); ent_b.release(); head.release(); pair_idx.release();
+        first_pair.release(); blocks_of.release(); blk_off.release(); tmp.release();
+    };
+    auto fail = [&](int code) { cleanup(); trs_sddmm_plan_destroy(p); return code; };
+    int rc = key_a.alloc(nnz);
+    if (!rc) rc = key_b.alloc(nnz);
+    if (!rc) rc = ent_a.alloc(nnz);
+    if (!rc) rc = ent_b.alloc(nnz);
+    if (!rc) rc = head.alloc(nnz);
+    if (!rc) rc = pair_idx.alloc(nnz);
+    if (!rc) rc = first_pair.alloc((size_t)W + 1);
+    if (!rc) rc = blocks_of.alloc((size_t)W + 1);
+    if (!rc) rc = blk_off.alloc((size_t)W + 1);
+    if (rc) return fail(rc);
+    auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
+    ksp_keys<<<grid(nnz), 256, 0, st>>>(rowptr, col, n_rows, nnz, key_a.p, ent_a.p);
+    int wbits = 1;
+    while ((1ll << wbits) < W) ++wbits;
+    cub::DoubleBuffer<unsigned long long> kb(key_a.p, key_b.p);
+    cub::DoubleBuffer<int> vb(ent_a.p, ent_b.p);
+    size_t bytes = 0, bytes2 = 0, bytes3 = 0;
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, bytes, kb, vb, (int)nnz, 0, 32 + wbits, st);
+    if (e == cudaSuccess) e = cub::DeviceScan::InclusiveSum(nullptr, bytes2, head.p, pair_idx.p, (int)nnz, st);
+    if (e == cudaSuccess) e = cub::DeviceScan::ExclusiveSum(nullptr, bytes3, blocks_of.p, blk_off.p, W + 1, st);
+    if (e != cudaSuccess) return fail((int)e);
+    if (bytes2 > bytes) bytes = bytes2;
+    if (bytes3 > bytes) bytes = bytes3;
+    rc = tmp.alloc(bytes + 16);
+    if (rc) return fail(rc);
+    e = cub::DeviceRadixSort::SortPairs(tmp.p, bytes, kb, vb, (int)nnz, 0, 32 + wbits, st);
+    if (e != cudaSuccess) return fail((int)e);
+    const unsigned long long* key = kb.Current();
+    const int* ent = vb.Current();
+    ksp_heads<<<grid(nnz), 256, 0, st>>>(key, nnz, head.p);
+    e = cub::DeviceScan::InclusiveSum(tmp.p, bytes, head.p, pair_idx.p, (int)nnz, st);  // pair id + 1
+    if (e != cudaSuccess) return fail((int)e);
+    int total_pairs = 0;
+    e = cudaMemcpyAsync(&total_pairs, pair_idx.p + (nnz - 1), sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail((int)e);
+    // pair_idx holds inclusive sums: pair id of sorted entry i = pair_idx[i] - 1.  ksp_window_pairs
+    // and ksp_fill only use differences against first_pair, which is taken from the same array.
+    e = cudaMemsetAsync(blocks_of.p, 0, sizeof(int) * ((size_t)W + 1), st);
+    if (e != cudaSuccess) return fail((int)e);
+    ksp_window_pairs<<<grid(W + 1), 256, 0, st>>>(key, pair_idx.p, nnz, total_pairs + 1, W, first_pair.p, blocks_of.p);
+    e = cub::DeviceScan::ExclusiveSum(tmp.p, bytes, blocks_of.p, blk_off.p, W + 1, st);
+    if (e != cudaSuccess) return fail((int)e);
+    int n_blocks = 0;
+    e = cudaMemcpyAsync(&n_blocks, blk_off.p + W, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail((int)e);
+    p->n_blocks = n_blocks;
+    p->n_pairs = total_pairs;
+    rc = p->blocks.alloc((size_t)n_blocks);
+    if (rc) return fail(rc);
+    ksp_init_blocks<<<grid((long long)n_blocks * 32), 256, 0, st>>>(p->blocks.p, n_blocks);
+    ksp_fill<<<grid(nnz), 256, 0, st>>>(key, ent, pair_idx.p, head.p, first_pair.p, blk_off.p, rowptr, n_rows, nnz,
+                                       p->blocks.p);
+    e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return fail((int)e);
+    cleanup();
+    *out = p;
+    return TRS_OK;
+}
+
+extern "C" int trs_sddmm_plan_info(const trs_sddmm_plan* p, long long* n_pairs, long long* n_blocks) {
+    if (!p) return TRS_E_ARG;
+    if (n_pairs) *n_pairs = p->n_pairs;
+    if (n_blocks) *n_blocks = p->n_blocks;
+    return TRS_OK;
+}
+
+extern "C" int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y, trs_half* out,
+                         int n_rows, int n_cols, int K, void* stream);
+
+extern "C" int trs_sddmm_plan_run(const trs_sddmm_plan* p, const trs_half* X, const trs_half* Y, trs_half* out, int K,
+                                  void* stream) {
+    if (!p || !X || !Y || K <= 0) return TRS_E_ARG;
+    if (p->nnz == 0) return TRS_OK;
+    if (!out) return TRS_E_ARG;
+    const bool tc = (K == 32 || K == 64 || K == 128) && (((uintptr_t)X & 15) == 0) && (((uintptr_t)Y & 15) == 0);
+    if (!tc) return trs_sddmm(p->rowptr, p->col, X, Y, out, p->n_rows, p->n_cols, K, stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long warps = trs::ceil_div64(p->n_blocks, trs::kSddmmBlocksPerWarp);
+    const unsigned grid = (unsigned)trs::ceil_div64(warps, 4);
+    if (K == 32)
+        trs::k_sddmm_tc<1><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, (__half*)out, p->n_rows);
+    else if (K == 64)
+        trs::k_sddmm_tc<2><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, (__half*)out, p->n_rows);
+    else
+        trs::k_sddmm_tc<4><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, (__half*)out, p->n_rows);
+    TRS_LAUNCH_CHECK();
+    return TRS_OK;
+}
 
 extern "C" int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y, trs_half* out,
                          int n_rows, int n_cols, int K, void* stream) {

@@ -8,8 +8,10 @@ from . import graphs  # noqa: F401
 from ._lib import TrsError, lib_path, load  # noqa: F401
 from .format import FORMAT_NAMES, Format  # noqa: F401
 from .spmm import SpmmPlan, spmm_forward_host, ResidentSpmm  # noqa: F401
-from .sddmm import sddmm  # noqa: F401
+from .sddmm import sddmm, SddmmPlan  # noqa: F401
 from .builder import build_format  # noqa: F401
 from .gcn import ShardedGCN2  # noqa: F401
 from . import shard  # noqa: F401
 from .dataset import GCN_dataset_tcu_sptc_cuda_online, edges_to_csr, kernel_tcu_sptc_cuda_online  # noqa: F401
+from .autograd import DifferentiableSpmm, transpose_csr  # noqa: F401
+from . import reorder  # noqa: F401

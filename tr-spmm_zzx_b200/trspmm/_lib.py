@@ -101,6 +101,12 @@ def load():
                                                    C.POINTER(TrsTiming)]
     lib.trs_sddmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
     lib.trs_spmm_status.argtypes = [vp, C.POINTER(i32)]
+    lib.trs_sddmm_plan_create.argtypes = [vp, vp, i32, i32, vp, C.POINTER(vp)]
+    lib.trs_sddmm_plan_run.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.trs_sddmm_plan_info.argtypes = [vp, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]
+    lib.trs_sddmm_plan_destroy.argtypes = [vp]
+    for name in ("trs_sddmm_plan_create", "trs_sddmm_plan_run", "trs_sddmm_plan_info", "trs_sddmm_plan_destroy"):
+        getattr(lib, name).restype = i32
     lib.trs_build_create.argtypes = [vp, vp, vp, i32, C.POINTER(TrsBuildConfig), vp, C.POINTER(vp)]
     lib.trs_build_destroy.argtypes = [vp]
     lib.trs_build_sizes.argtypes = [vp, C.POINTER(C.c_longlong)]
