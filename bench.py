@@ -407,7 +407,9 @@ def run_sddmm(args):
                        "call": "trs_sddmm_plan_run (pattern planned once)", "plan_ms": plan_ms,
                        "window_column_pairs": plan.n_pairs, "ms_per_step_unplanned_trs_sddmm": ms_unplanned},
             "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None, "kernel": "k_sddmm_tc"},
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": 184.4e6 if args.workload == "clustered" else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch (profiles/)",
+                         "kernel": "k_sddmm_tc_pipe"},
             "gpu_launches": args.steps, "clocks": clocks.summary()}
     if not args.no_cpu:
         from oracle import oracle as O
