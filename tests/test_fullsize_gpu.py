@@ -60,6 +60,35 @@ def test_full_size_properties(workload):
     assert 0 < int(diff_rows) < n
 
 
+@pytest.mark.parametrize("workload", ["clustered", "rmat20"])
+def test_planned_sddmm_full_size(workload):
+    """The planned tensor-core SDDMM at bench sizes: every entry written, all entries equal to the
+    entry-parallel kernel's within fp16 rounding, and 2 M sampled entries equal to fp32 dot products."""
+    from trspmm import SddmmPlan
+    dev = torch.device("cuda")
+    if workload == "clustered":
+        rp, col, _ = graphs.clustered_graph(262144, 128, 24, 4, seed=0, device=dev)
+    else:
+        rp, col, _ = graphs.rmat_graph(20, 16, seed=0, device=dev)
+    n, K = rp.numel() - 1, 64
+    g = torch.Generator(device=dev).manual_seed(3)
+    X = torch.randn(n, K, device=dev, generator=g).half()
+    Y = torch.randn(n, K, device=dev, generator=g).half()
+    plan = SddmmPlan(rp, col, n)
+    out = torch.full((col.numel(),), float("nan"), dtype=torch.float16, device=dev)
+    plan.run(X, Y, out=out)
+    assert not bool(torch.isnan(out).any())
+    plain = sddmm(rp, col, X, Y)
+    scale = float(plain.float().abs().max())
+    assert float((out.float() - plain.float()).abs().max()) <= 4e-3 * scale
+    rows = torch.repeat_interleave(torch.arange(n, device=dev), (rp[1:] - rp[:-1]).long())
+    pick = torch.randint(0, col.numel(), (2_000_000,), device=dev, generator=g)
+    ref = (X[rows[pick]].float() * Y[col[pick].long()].float()).sum(-1)
+    err = (out[pick].float() - ref).abs() / ref.abs().clamp_min(1e-2 * float(ref.abs().max()))
+    assert float(err.max()) <= 1e-2 and float(err.mean()) <= 1e-3
+    assert torch.equal(plan.run(X, Y), out)
+
+
 def test_sddmm_full_size_against_row_samples():
     dev = torch.device("cuda")
     rp, col, _ = graphs.clustered_graph(262144, 128, 24, 4, seed=0, device=dev)

@@ -455,9 +455,26 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
 //     (no bitmap decoding in the loop),
 //   * all shared-memory addresses are hoisted out of the loop.
 // ----------------------------------------------------------------------------------------------
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArgs a) {
-    using T = Tile<WARPS>;
+// Shared memory of the lean kernel: the A operand of a step needs 512 bytes at most (two expanded
+// TC blocks; a packed tile with its metadata is 288), which with 4 stages leaves room for 11 CTAs
+// of 128 threads per SM; the launch bound holds the register allocation to that (40 registers).
+template <int WARPS, int STAGES>
+struct LeanTile {
+    static constexpr int FS = WARPS * 32;
+    static constexpr int ROWB = FS * 2 + 16;
+    static constexpr int BBYTES = 16 * ROWB;
+    static constexpr int STAGE = BBYTES + 512;
+    static constexpr int SMEM = STAGE * STAGES + kIdxRing * 64;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int CPR = FS / 8;
+    static constexpr int MIN_CTAS = WARPS == 4 ? (STAGES >= 4 ? 11 : 12) : 1;
+};
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, LeanTile<WARPS, STAGES>::MIN_CTAS) k_window_spmm_lean(const KernelArgs a) {
+    using T = LeanTile<WARPS, STAGES>;
+    constexpr int kStages = STAGES;                 // shadows the file-wide stage count
+    constexpr int kIdxAhead = 2 * STAGES - 2;       // column ids are fetched this many steps ahead (ring of 8)
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -1414,8 +1431,20 @@ static int launch_window_kernel(const KernelArgs& a, int n_items, bool lean_ok, 
     dim3 grid(n_items, ceil_div(a.F, T::FS));
     static const bool use_lean = [] { const char* v = getenv("TRS_SPMM_KERNEL"); return !(v && strcmp(v, "cpasync_v1") == 0); }();
     if (aligned && lean_ok && use_lean) {
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
-        k_window_spmm_lean<WARPS><<<grid, T::THREADS, T::SMEM, st>>>(a);
+        static const int lean_stages = [] { const char* v = getenv("TRS_LEAN_STAGES"); return v && atoi(v) == 3 ? 3 : 4; }();
+        if (lean_stages == 3) {
+            using L = LeanTile<WARPS, 3>;
+            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
+            k_window_spmm_lean<WARPS, 3><<<grid, L::THREADS, L::SMEM, st>>>(a);
+        } else {
+            using L = LeanTile<WARPS, 4>;
+            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 4>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
+            k_window_spmm_lean<WARPS, 4><<<grid, L::THREADS, L::SMEM, st>>>(a);
+        }
     } else if (aligned) {
         TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
         k_window_spmm<WARPS, true><<<grid, T::THREADS, T::SMEM, st>>>(a);
