@@ -456,8 +456,12 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
 //   * all shared-memory addresses are hoisted out of the loop.
 // ----------------------------------------------------------------------------------------------
 // Shared memory of the lean kernel: the A operand of a step needs 512 bytes at most (two expanded
-// TC blocks; a packed tile with its metadata is 288), which with 4 stages leaves room for 11 CTAs
-// of 128 threads per SM; the launch bound holds the register allocation to that (40 registers).
+// TC blocks; a packed tile with its metadata is 288).  With 4 stages that would leave room for 11
+// CTAs of 128 threads per SM, but holding the register allocation to the 40 registers this needs
+// (a launch bound of 11, or 12 with 3 stages) was measured slower on B200 (3.80 vs 3.3 ms at R-MAT
+// scale 21, 0.174 vs 0.158 ms on the clustered case): the kernel then re-computes addresses it
+// otherwise keeps in registers.  So no minimum is requested (a minimum of 1 would let the compiler
+// take 74 registers: 6 CTAs per SM, 3.81 ms): 48 registers, 10 CTAs per SM.
 template <int WARPS, int STAGES>
 struct LeanTile {
     static constexpr int FS = WARPS * 32;
@@ -467,11 +471,10 @@ struct LeanTile {
     static constexpr int SMEM = STAGE * STAGES + kIdxRing * 64;
     static constexpr int THREADS = WARPS * 32;
     static constexpr int CPR = FS / 8;
-    static constexpr int MIN_CTAS = WARPS == 4 ? (STAGES >= 4 ? 11 : 12) : 1;
 };
 
 template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, LeanTile<WARPS, STAGES>::MIN_CTAS) k_window_spmm_lean(const KernelArgs a) {
+__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArgs a) {
     using T = LeanTile<WARPS, STAGES>;
     constexpr int kStages = STAGES;                 // shadows the file-wide stage count
     constexpr int kIdxAhead = 2 * STAGES - 2;       // column ids are fetched this many steps ahead (ring of 8)
