@@ -132,7 +132,8 @@ def make_matrix(workload, device):
 # DRAM bytes of one launch of the window kernel on one GPU (dram__bytes_read.sum +
 # dram__bytes_write.sum of single-metric, one-pass ncu captures of this very command; the
 # summaries under profiles/ give the commands).  Workloads not captured report null.
-MEASURED_TRAFFIC = {("rmat21", 128): 8.29e9 + 0.628e9, ("rmat20", 128): 1.728e9 + 0.269e9}
+MEASURED_TRAFFIC = {("rmat21", 128): 8.29e9 + 0.628e9, ("rmat20", 128): 1.728e9 + 0.269e9,
+                    ("clustered", 128): 273.9e6 + 55.9e6}
 
 
 def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):
