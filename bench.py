@@ -282,36 +282,66 @@ def run_ours(args, rank, world, local_rank):
     ms = e0.elapsed_time(e1) / args.steps
     status = plan.status()
 
-    # ---- e2e through the host-buffer C-ABI entry: B from pinned host memory, C back to the host
-    res = ResidentSpmm(fmt, max(m_local, 1), n, 16, F)
-    B_host = B.cpu().pin_memory()
-    C_host = torch.empty((max(m_local, 1), F), dtype=torch.float16).pin_memory()
+    # ---- e2e with HOST buffers: B from pinned host memory, C back to the host, every step
     e2e_steps = max(2, min(args.steps, 8))
-    res.forward(B_host, C_host)
-    sync_all()
-    # (a) one blocking call per step
-    t0 = time.perf_counter()
     h2d = d2h = 0.0
-    for _ in range(e2e_steps):
-        _, tm = res.forward(B_host, C_host)  # blocks until C is on the host
-        h2d += tm.h2d_ms; d2h += tm.d2h_ms
-    e2e_sync_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    # (b) the same calls as a stream (submit ... wait): every step still copies its own B in and
-    # its own C out; two host buffers of each alternate, as a caller with a producer would hold
-    B_hosts = [B_host, B_host.clone().pin_memory()]
-    C_hosts = [C_host, torch.empty_like(C_host).pin_memory()]
-    for i in range(2):
-        res.submit(B_hosts[i], C_hosts[i])
-    res.wait()
-    sync_all()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        res.submit(B_hosts[i & 1], C_hosts[i & 1])
-    res.wait()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    if not torch.equal(C_hosts[0], C_hosts[1]):
-        raise RuntimeError("pipelined calls disagree with each other")
-    res.close()
+    if world == 1:
+        # the host-buffer C-ABI entries of one GPU
+        res = ResidentSpmm(fmt, max(m_local, 1), n, 16, F)
+        B_host = B.cpu().pin_memory()
+        C_host = torch.empty((max(m_local, 1), F), dtype=torch.float16).pin_memory()
+        res.forward(B_host, C_host)
+        sync_all()
+        # (a) one blocking call per step
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            _, tm = res.forward(B_host, C_host)  # blocks until C is on the host
+            h2d += tm.h2d_ms; d2h += tm.d2h_ms
+        e2e_sync_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        # (b) the same calls as a stream (submit ... wait): every step still copies its own B in and
+        # its own C out; two host buffers of each alternate, as a caller with a producer would hold
+        B_hosts = [B_host, B_host.clone().pin_memory()]
+        C_hosts = [C_host, torch.empty_like(C_host).pin_memory()]
+        for i in range(2):
+            res.submit(B_hosts[i], C_hosts[i])
+        res.wait()
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            res.submit(B_hosts[i & 1], C_hosts[i & 1])
+        res.wait()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        res.close()
+        e2e_call = ("trs_resident_submit x steps + trs_resident_wait (format resident; every step copies "
+                    "B host->device and C device->host; consecutive steps overlap on three streams)")
+        e2e_block_call = "trs_resident_forward, one blocking call per step"
+    else:
+        # every rank copies its 1/N slice of B over PCIe, the slices are all-gathered over NVLink,
+        # each rank multiplies its windows and copies its rows of C back
+        sh = shard.ShardedHostSpmm(fmt, m_local, n, F, rank, world)
+        k0, k1 = sh.my_rows()
+        B_hosts = [B[k0:k1].cpu().pin_memory() for _ in range(2)]
+        C_hosts = [torch.empty((max(m_local, 1), F), dtype=torch.float16).pin_memory() for _ in range(2)]
+        for i in range(2):
+            sh.submit(B_hosts[i], C_hosts[i])
+        sh.wait()
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            sh.submit(B_hosts[i & 1], C_hosts[i & 1])
+            sh.wait()
+        e2e_sync_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            sh.submit(B_hosts[i & 1], C_hosts[i & 1])
+        sh.wait()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        e2e_call = (f"ShardedHostSpmm.submit x steps + wait: each rank copies 1/{world} of B host->device, NCCL "
+                    "all-gather over NVLink, own windows, own rows of C device->host; steps overlap on four streams")
+        e2e_block_call = "ShardedHostSpmm.submit + wait per step"
+    if not torch.equal(C_hosts[0], C_hosts[1]) or not torch.equal(C_hosts[0], out.cpu()):
+        raise RuntimeError("host-buffer calls disagree with the device-resident result")
 
     kept = torch.tensor([float(kept_local), ms, e2e_ms, e2e_sync_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -346,12 +376,11 @@ def run_ours(args, rank, world, local_rank):
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch (profiles/)",
                          "kernel": "k_window_spmm_lean"},
             "e2e": {"value": 2.0 * kept_total * F / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
-                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": n * F * 2, "d2h_bytes_per_step": max(m_local, 1) * F * 2,
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": n * F * 2, "d2h_bytes_per_step": n * F * 2,
                     "h2d_ms": h2d / e2e_steps, "d2h_ms": d2h / e2e_steps, "steps": e2e_steps,
-                    "call": "trs_resident_submit x steps + trs_resident_wait (format resident; every step copies "
-                            "B host->device and C device->host; consecutive steps overlap on three streams)",
+                    "call": e2e_call,
                     "blocking_call": {"value": 2.0 * kept_total * F / (e2e_sync_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
-                                      "ms_per_step": e2e_sync_ms, "call": "trs_resident_forward, one blocking call per step"}},
+                                      "ms_per_step": e2e_sync_ms, "call": e2e_block_call}},
             "gpu_launches": plan.launches * args.steps,
             "clocks": clocks.summary(), "kernel_status": status,
         }
@@ -481,7 +510,7 @@ def run_gcn(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="rmat21", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

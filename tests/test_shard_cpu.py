@@ -138,3 +138,12 @@ def test_rank_failure_is_seen_on_the_host():
         p.join(timeout=120)
     assert procs[1].exitcode != 0
     assert q.get(timeout=10).startswith("error")
+
+
+def test_even_row_split_covers_all_rows():
+    from trspmm.shard import even_row_split
+    for n, w in ((10, 1), (10, 3), (2097152, 8), (7, 8), (16, 4)):
+        per, padded = even_row_split(n, w)
+        assert per * w == padded and padded >= n and padded - n < w + per
+        covered = sum(max(0, min((r + 1) * per, n) - r * per) for r in range(w))
+        assert covered == n

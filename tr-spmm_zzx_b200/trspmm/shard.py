@@ -77,3 +77,81 @@ def shard_for_rank(rowptr, col, val, rank: int, world: int, window: int = 16):
     cuts = balanced_window_cuts(rowptr, world, window)
     r0, r1 = cuts[rank], cuts[rank + 1]
     return (r0, r1), slice_csr(rowptr, col, val, r0, r1)
+
+
+def even_row_split(n_rows: int, world: int):
+    """Rows per rank and padded total for an equal-sized split of a dense [n_rows, F] operand
+    (the all-gather wants equal pieces; the padding rows are never read by a kernel)."""
+    per = (n_rows + world - 1) // world
+    return per, per * world
+
+
+class ShardedHostSpmm:
+    """Host-buffer SpMM on `world` GPUs of one box, for a stream of calls over one matrix.
+
+    Without it every rank would pull the whole dense operand B over PCIe (world copies of the same
+    bytes through the host's memory system).  Here each rank copies only its 1/world slice of B
+    from pinned host memory, the slices are exchanged with one in-place NCCL all-gather over NVLink,
+    each rank multiplies its own row windows, and copies its rows of C back.  Four streams (input
+    copy, all-gather, kernels, output copy) and two buffer slots let consecutive calls overlap.
+
+    The reference has no multi-GPU path; the single-GPU call this extends is
+    spmm_forward_fp16_tcu_cuda_sptc_mma_parallel_online (mGCN_online.cpp:760), which copies B in and
+    C out on every call.
+    """
+
+    def __init__(self, fmt, m_local: int, n_cols: int, F: int, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        from .spmm import SpmmPlan
+        self.dist, self.group = dist, group
+        self.rank, self.world, self.F = rank, world, F
+        self.m_local, self.n_cols = max(m_local, 1), n_cols
+        self.dev = fmt.device
+        self.plan = SpmmPlan(fmt, self.m_local, n_cols)
+        self.per, padded = even_row_split(n_cols, world)
+        self.B = [torch.zeros((padded, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
+        self.C = [torch.empty((self.m_local, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
+        self.s_in, self.s_comm, self.s_k, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(4))
+        ev = lambda: torch.cuda.Event()  # noqa: E731
+        self.in_done, self.comm_done, self.k_done, self.out_done = ([ev(), ev()] for _ in range(4))
+        self.seq = 0
+        self._keep = []
+
+    def my_rows(self):
+        """[begin, end) rows of B this rank is expected to provide."""
+        b = self.rank * self.per
+        return b, min(b + self.per, self.n_cols)
+
+    def submit(self, B_slice_host: torch.Tensor, C_host: torch.Tensor):
+        """B_slice_host: pinned fp16 [rows of my_rows(), F]; C_host: pinned fp16 [m_local, F]."""
+        s = self.seq & 1
+        b0, b1 = self.my_rows()
+        if B_slice_host.shape != (b1 - b0, self.F) or C_host.shape != (self.m_local, self.F):
+            raise ValueError("slice shapes do not match this rank's share")
+        self._keep.append((B_slice_host, C_host))
+        Bs, Cs = self.B[s], self.C[s]
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(self.k_done[s])           # the kernels two calls back are done with this slot
+            Bs[b0:b1].copy_(B_slice_host, non_blocking=True)
+            self.in_done[s].record(self.s_in)
+        with torch.cuda.stream(self.s_comm):
+            self.s_comm.wait_event(self.in_done[s])
+            if self.world > 1:
+                mine = Bs[self.rank * self.per:(self.rank + 1) * self.per]
+                self.dist.all_gather_into_tensor(Bs, mine, group=self.group)   # in place: `mine` is its own piece of Bs
+            self.comm_done[s].record(self.s_comm)
+        with torch.cuda.stream(self.s_k):
+            self.s_k.wait_event(self.comm_done[s])
+            self.s_k.wait_event(self.out_done[s])           # the output copy two calls back has drained this slot
+            self.plan.run(Bs[:self.n_cols], out=Cs)
+            self.k_done[s].record(self.s_k)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.k_done[s])
+            C_host.copy_(Cs, non_blocking=True)
+            self.out_done[s].record(self.s_out)
+        self.seq += 1
+
+    def wait(self):
+        for st in (self.s_in, self.s_comm, self.s_k, self.s_out):
+            st.synchronize()
+        self._keep.clear()
