@@ -217,78 +217,12 @@ __global__ void ksp_fill(const unsigned long long* __restrict__ key, const int* 
 
 constexpr int kSddmmBlocksPerWarp = 64;
 
-// U = blocks whose Y rows a warp requests before it consumes any; MINB = resident CTAs per SM the
-// register allocation is held to.  Many light warps beat few deeply pipelined ones here.
-template <int KCH, int U, int MINB>  // K = 32 * KCH
-__global__ void __launch_bounds__(128, MINB) k_sddmm_tc(const SddmmBlock* __restrict__ blk, long long n_blocks,
-                                                        const __half* __restrict__ X, const __half* __restrict__ Y,
-                                                        __half* __restrict__ out, int n_rows, int blocks_per_warp) {
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long b0 = warp * blocks_per_warp;
-    if (b0 >= n_blocks) return;
-    const long long b1 = min(b0 + (long long)blocks_per_warp, n_blocks);
-    constexpr int ROW16 = KCH * 4;  // 16-byte units per row
-    const uint4* Xq = (const uint4*)X + t;
-    const uint4* Yq = (const uint4*)Y + t;
-
-    int cur_w = -1;
-    uint4 xa[KCH], xb[KCH];  // X[row g], X[row g + 8]: this lane's 16 bytes of every chunk
-#pragma unroll
-    for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
-
-    for (long long bb = b0; bb < b1; bb += U) {
-        uint4 yv[U][KCH];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (bb + u < b1) {
-                const int c = max(__ldg(&blk[bb + u].col[g]), 0);  // unused slot: any valid row, result not stored
-#pragma unroll
-                for (int ch = 0; ch < KCH; ++ch) yv[u][ch] = __ldg(Yq + (size_t)c * ROW16 + ch * 4);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (bb + u >= b1) break;
-            const SddmmBlock* b = blk + bb + u;
-            const int w = __ldg(&b->window);
-            if (w != cur_w) {  // warp-uniform
-                cur_w = w;
-                const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
-#pragma unroll
-                for (int ch = 0; ch < KCH; ++ch) {
-                    xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
-                    xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
-                }
-            }
-            float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ch = 0; ch < KCH; ++ch) {
-                mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, yv[u][ch].x, yv[u][ch].y);
-                mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, yv[u][ch].z, yv[u][ch].w);
-            }
-            // d[0], d[1]: row g, slots 2t, 2t+1;  d[2], d[3]: row g + 8
-            const unsigned wa = __ldg(&b->bits[g >> 2]), wb = __ldg(&b->bits[(g >> 2) + 2]);
-            const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
-            const int n0 = 2 * t;
-            if ((ba >> n0) & 3u) {
-                const int s = __ldg(&b->start[g]) + __popc(ba & ((1u << n0) - 1u));
-                if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
-                if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
-            }
-            if ((bbits >> n0) & 3u) {
-                const int s = __ldg(&b->start[g + 8]) + __popc(bbits & ((1u << n0) - 1u));
-                if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
-                if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
-            }
-        }
-    }
-}
-
-// Same work, one block at a time with an explicit pipeline: the column ids run two blocks ahead
-// of the MMAs and the Y rows one block, so the two dependent loads of a block (its record, then
-// the rows the record names) overlap with the previous blocks' work at a cost of 9 registers.
+// One warp walks kSddmmBlocksPerWarp consecutive blocks, one block at a time, with an explicit
+// pipeline: the column ids run two blocks ahead of the MMAs and the Y rows one block, so the two
+// dependent loads of a block (its record, then the rows the record names) overlap with the
+// previous blocks' work at a cost of 9 registers.  MINB holds the register allocation to MINB CTAs
+// of 128 threads per SM: many light warps measured faster than deeper per-warp unrolls (four or
+// eight blocks of Y rows requested at once cost 90-122 registers and ran 20-40 % slower).
 template <int KCH, int MINB>
 __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_pipe(const SddmmBlock* __restrict__ blk, long long n_blocks,
                                                              const __half* __restrict__ X, const __half* __restrict__ Y,
@@ -483,25 +417,13 @@ extern "C" int trs_sddmm_plan_run(const trs_sddmm_plan* p, const trs_half* X, co
     const bool tc = (K == 32 || K == 64 || K == 128) && (((uintptr_t)X & 15) == 0) && (((uintptr_t)Y & 15) == 0);
     if (!tc) return trs_sddmm(p->rowptr, p->col, X, Y, out, p->n_rows, p->n_cols, K, stream);
     cudaStream_t st = (cudaStream_t)stream;
-    static const int variant = [] { const char* v = getenv("TRS_SDDMM_VARIANT"); return v ? atoi(v) : 5; }();
     static const int bpw = [] { const char* v = getenv("TRS_SDDMM_BPW"); return v && atoi(v) > 0 ? atoi(v) : trs::kSddmmBlocksPerWarp; }();
     const long long warps = trs::ceil_div64(p->n_blocks, bpw);
     const unsigned grid = (unsigned)trs::ceil_div64(warps, 4);
-#define TRS_SDDMM_LAUNCH(KCH, U, MINB)                                                                            \
-    trs::k_sddmm_tc<KCH, U, MINB><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, \
-                                                        (__half*)out, p->n_rows, bpw)
-    if (K == 32) TRS_SDDMM_LAUNCH(1, 4, 1);
-    else if (K == 128) TRS_SDDMM_LAUNCH(4, 2, 1);
-    else if (variant == 1) TRS_SDDMM_LAUNCH(2, 2, 8);
-    else if (variant == 2) TRS_SDDMM_LAUNCH(2, 4, 8);
-    else if (variant == 3) TRS_SDDMM_LAUNCH(2, 8, 1);
-    else if (variant == 4) TRS_SDDMM_LAUNCH(2, 1, 8);
-    else if (variant == 5) trs::k_sddmm_tc_pipe<2, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, (__half*)out, p->n_rows, bpw);
-    else if (variant == 6) trs::k_sddmm_tc_pipe<2, 10><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, (const __half*)X, (const __half*)Y, (__half*)out, p->n_rows, bpw);
-    else if (variant == 7) TRS_SDDMM_LAUNCH(2, 1, 10);
-    else if (variant == 8) TRS_SDDMM_LAUNCH(2, 1, 12);
-    else TRS_SDDMM_LAUNCH(2, 4, 1);
-#undef TRS_SDDMM_LAUNCH
+    const __half *x = (const __half*)X, *y = (const __half*)Y;
+    if (K == 32) trs::k_sddmm_tc_pipe<1, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+    else if (K == 64) trs::k_sddmm_tc_pipe<2, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+    else trs::k_sddmm_tc_pipe<4, 5><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     TRS_LAUNCH_CHECK();
     return TRS_OK;
 }
