@@ -291,103 +291,6 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_pipe(const SddmmBlock* _
     }
 }
 
-// Ring variant: the gathered Y pieces of the next DEPTH blocks wait in a shared-memory FIFO that
-// is private to each lane (a lane copies with cp.async exactly the 16-byte pieces it will later
-// read, at address stage + (chunk * 32 + lane) * 16: conflict-free, and no cross-lane visibility
-// to wait for), so a warp keeps DEPTH blocks of row gathers in flight without paying registers
-// for them.  Column ids run two blocks ahead of the copies, the rest of a block's record one block
-// ahead of its MMAs.
-template <int KCH, int DEPTH>
-__global__ void __launch_bounds__(128, 8) k_sddmm_tc_ring(const SddmmBlock* __restrict__ blk, long long n_blocks,
-                                                       const __half* __restrict__ X, const __half* __restrict__ Y,
-                                                       __half* __restrict__ out, int n_rows, int blocks_per_warp) {
-    extern __shared__ __align__(16) unsigned char ring_smem[];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + wid;
-    const long long b0 = warp * blocks_per_warp;
-    if (b0 >= n_blocks) return;
-    const long long b1 = min(b0 + (long long)blocks_per_warp, n_blocks);
-    constexpr int ROW16 = KCH * 4;
-    constexpr int STAGE = KCH * 32 * 16;  // bytes of one block's Y pieces for a warp
-    const uint4* Xq = (const uint4*)X + t;
-    const uint4* Yq = (const uint4*)Y + t;
-    unsigned char* my = ring_smem + (size_t)wid * DEPTH * STAGE + lane * 16;
-    const uint32_t my_s = smem_u32(my);
-
-    auto col_of = [&](long long b) { return b < b1 ? max(__ldg(&blk[b].col[g]), 0) : 0; };
-    auto issue = [&](long long b, int c) {  // copies of block b into stage b % DEPTH
-        if (b < b1) {
-            const uint32_t dst = my_s + (uint32_t)((b - b0) % DEPTH) * STAGE;
-#pragma unroll
-            for (int ch = 0; ch < KCH; ++ch) cp_async16(dst + ch * 512, Yq + (size_t)c * ROW16 + ch * 4, 16);
-        }
-        cp_async_commit();
-    };
-
-    int cur_w = -1;
-    uint4 xa[KCH], xb[KCH];
-#pragma unroll
-    for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
-
-    // prologue: the first DEPTH blocks' copies, the ids of the two after them, the first record
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) issue(b0 + d, col_of(b0 + d));
-    int c1 = col_of(b0 + DEPTH), c2 = col_of(b0 + DEPTH + 1);
-    int m_w = __ldg(&blk[b0].window);
-    unsigned m_a = __ldg(&blk[b0].bits[g >> 2]), m_b = __ldg(&blk[b0].bits[(g >> 2) + 2]);
-    int m_sa = __ldg(&blk[b0].start[g]), m_sb = __ldg(&blk[b0].start[g + 8]);
-
-    for (long long bb = b0; bb < b1; ++bb) {
-        cp_async_wait<DEPTH - 1>();  // block bb's pieces have landed (own copies: no warp sync needed)
-        uint4 y[KCH];
-        const unsigned char* src = my + (size_t)((bb - b0) % DEPTH) * STAGE;
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) y[ch] = *(const uint4*)(src + ch * 512);
-        issue(bb + DEPTH, c1);       // refill the stage just read
-        c1 = c2;
-        c2 = col_of(bb + DEPTH + 2);
-        const int w = m_w, sa = m_sa, sb = m_sb;
-        const unsigned wa = m_a, wb = m_b;
-        if (bb + 1 < b1) {           // next block's record, one block ahead
-            const SddmmBlock* nb = blk + bb + 1;
-            m_w = __ldg(&nb->window);
-            m_a = __ldg(&nb->bits[g >> 2]);
-            m_b = __ldg(&nb->bits[(g >> 2) + 2]);
-            m_sa = __ldg(&nb->start[g]);
-            m_sb = __ldg(&nb->start[g + 8]);
-        }
-        if (w != cur_w) {  // warp-uniform
-            cur_w = w;
-            const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
-#pragma unroll
-            for (int ch = 0; ch < KCH; ++ch) {
-                xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
-                xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
-            }
-        }
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) {
-            mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y[ch].x, y[ch].y);
-            mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y[ch].z, y[ch].w);
-        }
-        const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
-        const int n0 = 2 * t;
-        if ((ba >> n0) & 3u) {
-            const int s = sa + __popc(ba & ((1u << n0) - 1u));
-            if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
-            if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
-        }
-        if ((bbits >> n0) & 3u) {
-            const int s = sb + __popc(bbits & ((1u << n0) - 1u));
-            if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
-            if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
-        }
-    }
-    cp_async_wait<0>();
-}
-
 }  // namespace trs
 
 struct trs_sddmm_plan {
@@ -518,23 +421,6 @@ extern "C" int trs_sddmm_plan_run(const trs_sddmm_plan* p, const trs_half* X, co
     const long long warps = trs::ceil_div64(p->n_blocks, bpw);
     const unsigned grid = (unsigned)trs::ceil_div64(warps, 4);
     const __half *x = (const __half*)X, *y = (const __half*)Y;
-    static const int ring = [] { const char* v = getenv("TRS_SDDMM_RING"); return v ? atoi(v) : 0; }();
-    if (ring > 0 && K == 64) {
-        if (ring == 8) {
-            constexpr int SM = 4 * 8 * 2 * 512;
-            TRS_CUDA(cudaFuncSetAttribute(trs::k_sddmm_tc_ring<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM));
-            trs::k_sddmm_tc_ring<2, 8><<<grid, 128, SM, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-        } else if (ring == 6) {
-            constexpr int SM = 4 * 6 * 2 * 512;
-            TRS_CUDA(cudaFuncSetAttribute(trs::k_sddmm_tc_ring<2, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM));
-            trs::k_sddmm_tc_ring<2, 6><<<grid, 128, SM, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-        } else {
-            constexpr int SM = 4 * 4 * 2 * 512;
-            trs::k_sddmm_tc_ring<2, 4><<<grid, 128, SM, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-        }
-        TRS_LAUNCH_CHECK();
-        return TRS_OK;
-    }
     if (K == 32) trs::k_sddmm_tc_pipe<1, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     else if (K == 64) trs::k_sddmm_tc_pipe<2, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     else trs::k_sddmm_tc_pipe<4, 5><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);

@@ -768,225 +768,6 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) k_window_spmm_bulk(const Ker
     finish_item(acc, it, a, fbase, wid, g, t);
 }
 
-// ----------------------------------------------------------------------------------------------
-// Lane-private FIFO variant (F % 8 == 0, 16-byte aligned arrays): no block barrier and no
-// ldmatrix.  A warp owns a 64-feature slab of one work item.  For every k-step each lane needs
-// 16 bytes from four of the sixteen gathered B rows (rows 2t, 2t+1, 2t+8, 2t+9 of the step,
-// features 8g..8g+7 of the slab: eight lanes cover 128 contiguous bytes of a row) plus its own A
-// fragment; two byte permutes per n-block turn the four pieces into the B fragments of
-// mma m16n8k16 — column n = g of n-block j is feature 8g + j, a permutation of the slab that only
-// the epilogue has to know.  Every lane copies exactly the bytes it will consume itself with
-// cp.async into its own slots of a shared-memory FIFO (address stage + (piece * 32 + lane) * 16:
-// conflict-free, and nothing to synchronise between lanes), FIFO_DEPTH k-steps ahead.  Only the
-// column ids are shared by the warp; they run ahead through a small ring, ordered by __syncwarp.
-// Accumulators: acc[j][2h + i] = row g + 8h, feature slab + 16t + 8i + j, i.e. every lane ends up
-// with 16 contiguous features of two rows and writes them with 16-byte stores.
-// ----------------------------------------------------------------------------------------------
-constexpr int kFifoIdBlocks = 4;      // ring of id blocks per warp, 8 k-steps (512 bytes) each
-constexpr int kFifoStage = 5 * 512;   // per warp and k-step: 4 B pieces + 1 A piece of 16 bytes per lane
-
-template <int DEPTH, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_fifo(const KernelArgs a) {
-    static_assert(DEPTH >= 2 && DEPTH <= 8, "the id ring runs 16 steps ahead, the FIFO at most 8");
-    extern __shared__ __align__(16) unsigned char fifo_smem[];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int fw = (blockIdx.y * WARPS + wid) * 64;   // first feature of this warp's slab
-    if (fw >= a.F) return;                            // no block-wide barrier anywhere below
-
-    const Item it = a.items[blockIdx.x];
-    const int nsteps = it.step_end - it.step_begin;
-
-    const bool fin = fw + 8 * g < a.F;                // this lane's 8 features exist
-    const uint32_t pitch16 = fin ? ((uint32_t)a.F >> 3) : 0u;
-    const uint4* zq = (const uint4*)a.zeros;
-    const uint4* Bq = fin ? (const uint4*)a.B + ((uint32_t)fw >> 3) + g : zq;
-
-    constexpr int WARP_BYTES = DEPTH * kFifoStage + kFifoIdBlocks * 512;
-    unsigned char* wbase = fifo_smem + (size_t)wid * WARP_BYTES;
-    unsigned char* my = wbase + lane * 16;                       // + stage * kFifoStage + piece * 512
-    const uint32_t my_s = smem_u32(my);
-    const int* ids = (const int*)(wbase + DEPTH * kFifoStage);   // [block % 4][step % 8][16]
-    const uint32_t ids_s = smem_u32(ids);
-
-    float acc[8][4];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-
-    // column ids of k-steps [8 blk, 8 blk + 8) -> ring slot blk % kFifoIdBlocks; lane = (step, quarter)
-    auto load_ids = [&](int blk) {
-        const int m = blk * 8 + (lane >> 2), q = lane & 3;
-        if (m < nsteps) {
-            const int s = it.step_begin + m;
-            const int off = (((blk & (kFifoIdBlocks - 1)) * 8 + (lane >> 2)) * 16 + q * 4) * 4;
-            if (s < it.ntiles) {
-                cp_async16(ids_s + off, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + q * 4, 16);
-            } else {
-                const int b = it.blk0 + 2 * (s - it.ntiles) + (q >> 1);
-                if (b < it.blk_end) cp_async16(ids_s + off, a.f.t_column + (size_t)b * 8 + (q & 1) * 4, 16);
-                else *(int4*)((unsigned char*)ids + off) = make_int4(-1, -1, -1, -1);
-            }
-        }
-    };
-
-    // all copies of k-step j into FIFO stage j % DEPTH (ids of step j must be visible)
-    auto issue = [&](int j) {
-        if (j < nsteps) {
-            const uint32_t dst = my_s + (uint32_t)(j % DEPTH) * kFifoStage;
-            const int* cols = ids + (((j >> 3) & (kFifoIdBlocks - 1)) * 8 + (j & 7)) * 16;
-            const int2 ca = *(const int2*)(cols + 2 * t);
-            const int2 cb = *(const int2*)(cols + 8 + 2 * t);
-            cp_async16(dst, ca.x >= 0 ? Bq + (uint32_t)ca.x * pitch16 : zq, 16);
-            cp_async16(dst + 512, ca.y >= 0 ? Bq + (uint32_t)ca.y * pitch16 : zq, 16);
-            cp_async16(dst + 1024, cb.x >= 0 ? Bq + (uint32_t)cb.x * pitch16 : zq, 16);
-            cp_async16(dst + 1536, cb.y >= 0 ? Bq + (uint32_t)cb.y * pitch16 : zq, 16);
-            const int s = it.step_begin + j;
-            if (s < it.ntiles) {
-                const size_t tile = (size_t)(it.tile0 + s);
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst + 2048),
-                             "l"(a.f.s_packed_a + tile * 64 + lane * 2));
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst + 2048 + 8),
-                             "l"(a.f.s_packed_meta + tile * 8 + g));
-            } else {
-                const int b = it.blk0 + 2 * (s - it.ntiles);
-                const uint32_t* d0 = (const uint32_t*)(a.tc_dense + (size_t)b * 128);
-                const bool two = b + 1 < it.blk_end;
-                const uint32_t* z = (const uint32_t*)a.zeros;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst + 2048), "l"(d0 + g * 4 + t));
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst + 2048 + 4), "l"(d0 + (g + 8) * 4 + t));
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst + 2048 + 8),
-                             "l"(two ? d0 + 64 + g * 4 + t : z));
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst + 2048 + 12),
-                             "l"(two ? d0 + 64 + (g + 8) * 4 + t : z));
-            }
-        }
-        cp_async_commit();
-    };
-
-    // Group accounting: the prologue commits 2 id groups and DEPTH step groups, iteration j commits
-    // one more (step j + DEPTH, plus an id block when j % 8 == 0).  Waiting until at most DEPTH - 1
-    // groups are pending at iteration j therefore completes step j; an id block is requested 16
-    // steps before its first step and read DEPTH <= 8 steps before it, so it has landed as well.
-    load_ids(0);
-    cp_async_commit();
-    load_ids(1);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncwarp();
-#pragma unroll
-    for (int u = 0; u < DEPTH; ++u) issue(u);
-    for (int j = 0; j < nsteps; ++j) {
-        if ((j & 7) == 0) load_ids((j >> 3) + 2);   // joins this iteration's group
-        cp_async_wait<DEPTH - 1>();
-        if ((j & 7) == 0) __syncwarp();             // id blocks are shared by the warp
-        const unsigned char* src = my + (size_t)(j % DEPTH) * kFifoStage;
-        const uint4 r0 = *(const uint4*)(src), r1 = *(const uint4*)(src + 512);
-        const uint4 r2 = *(const uint4*)(src + 1024), r3 = *(const uint4*)(src + 1536);
-        const uint4 av = *(const uint4*)(src + 2048);
-        issue(j + DEPTH);                            // refills the stage just read
-        const bool sparse = it.step_begin + j < it.ntiles;
-        const uint32_t* p0 = (const uint32_t*)&r0;
-        const uint32_t* p1 = (const uint32_t*)&r1;
-        const uint32_t* p2 = (const uint32_t*)&r2;
-        const uint32_t* p3 = (const uint32_t*)&r3;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const uint32_t sel = (n & 1) ? 0x7632u : 0x5410u;
-            const uint32_t b0 = __byte_perm(p0[n >> 1], p1[n >> 1], sel);
-            const uint32_t b1 = __byte_perm(p2[n >> 1], p3[n >> 1], sel);
-            if (sparse) mma_sp_16816(acc[n], av.x, av.y, b0, b1, av.z);
-            else mma_16816(acc[n], av.x, av.y, av.z, av.w, b0, b1);
-        }
-    }
-    cp_async_wait<0>();
-
-    // ---- CSR remainder parts of the window (first item only) -----------------------------------
-    const int w = it.window;
-    const size_t F = (size_t)a.F;
-    const int f0 = fw + 16 * t;  // this lane's 16 contiguous features
-    if (it.step_begin == 0) {
-        for (int pass = 0; pass < 2; ++pass) {
-            const int pb = pass ? a.wr.cs_begin[w] : a.wr.c_begin[w];
-            const int pe = pass ? a.wr.cs_end[w] : a.wr.c_end[w];
-            const int* roff = pass ? a.f.cs_row_offset : a.f.c_row_offset;
-            const int* rrow = pass ? a.f.cs_row : a.f.c_row;
-            const int* rcol = pass ? a.f.cs_column : a.f.c_column;
-            const __half* rval = (const __half*)(pass ? a.f.cs_value : a.f.c_value);
-            for (int p = pb; p < pe; ++p) {
-                const int lr = rrow[p] - w * a.window;
-                if ((lr & 7) != g || lr < 0 || lr >= 16) continue;
-                const int hi = lr >> 3;
-                for (int e = roff[p]; e < roff[p + 1]; ++e) {
-                    const float v = __half2float(rval[e]);
-                    const __half* brow = a.B + (size_t)rcol[e] * F;
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int f = f0 + 8 * i;
-                        if (f >= a.F) continue;
-                        const uint4 q = __ldg((const uint4*)(brow + f));
-                        const __half2* qh = (const __half2*)&q;
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const float2 x = __half22float2(qh[jj]);
-                            if (hi) { acc[2 * jj][2 + i] += v * x.x; acc[2 * jj + 1][2 + i] += v * x.y; }
-                            else { acc[2 * jj][i] += v * x.x; acc[2 * jj + 1][i] += v * x.y; }
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    // ---- the single write of the item's result -----------------------------------------------------
-    if (it.slot >= 0) {  // slice of a split window: fp32 partial sums
-        float* dst = a.scratch + (size_t)it.slot * 16 * F;
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int f = f0 + 8 * i;
-                if (f >= a.F) continue;
-                float* d = dst + (size_t)(g + 8 * h) * F + f;
-                *(float4*)d = make_float4(acc[0][2 * h + i], acc[1][2 * h + i], acc[2][2 * h + i], acc[3][2 * h + i]);
-                *(float4*)(d + 4) = make_float4(acc[4][2 * h + i], acc[5][2 * h + i], acc[6][2 * h + i], acc[7][2 * h + i]);
-            }
-        return;
-    }
-    if (a.relu) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[j][i] = fmaxf(acc[j][i], 0.f);
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int lr = g + 8 * h;
-        const long long row = (long long)w * a.window + lr;
-        if (lr >= a.window || row >= a.m_rows) continue;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int f = f0 + 8 * i;
-            if (f >= a.F) continue;
-            if (a.out_half) {
-                uint4 v;
-                __half2 h0 = __floats2half2_rn(acc[0][2 * h + i], acc[1][2 * h + i]);
-                __half2 h1 = __floats2half2_rn(acc[2][2 * h + i], acc[3][2 * h + i]);
-                __half2 h2 = __floats2half2_rn(acc[4][2 * h + i], acc[5][2 * h + i]);
-                __half2 h3 = __floats2half2_rn(acc[6][2 * h + i], acc[7][2 * h + i]);
-                v.x = *(const uint32_t*)&h0; v.y = *(const uint32_t*)&h1;
-                v.z = *(const uint32_t*)&h2; v.w = *(const uint32_t*)&h3;
-                __stcs((uint4*)((__half*)a.C + (size_t)row * F + f), v);
-            } else {
-                float* d = (float*)a.C + (size_t)row * F + f;
-                __stcs((float4*)d, make_float4(acc[0][2 * h + i], acc[1][2 * h + i], acc[2][2 * h + i], acc[3][2 * h + i]));
-                __stcs((float4*)(d + 4), make_float4(acc[4][2 * h + i], acc[5][2 * h + i], acc[6][2 * h + i], acc[7][2 * h + i]));
-            }
-        }
-    }
-}
-
 // Expands the bitmap + packed values of every TC block into a dense 16x8 fp16 tile.
 __global__ void k_expand_tc(const long long* __restrict__ t_binary, const int* __restrict__ t_block_offset,
                             const __half* __restrict__ t_value, int blocks, __half* __restrict__ dense) {
@@ -1652,30 +1433,6 @@ static int launch_window_kernel(const KernelArgs& a, int n_items, bool lean_ok, 
     const bool aligned = (a.F % 8 == 0) && (((uintptr_t)a.B & 15) == 0);
     dim3 grid(n_items, ceil_div(a.F, T::FS));
     static const bool use_lean = [] { const char* v = getenv("TRS_SPMM_KERNEL"); return !(v && strcmp(v, "cpasync_v1") == 0); }();
-    static const int fifo_depth = [] {
-        const char* v = getenv("TRS_SPMM_KERNEL");
-        if (!v || strncmp(v, "fifo", 4) != 0) return 0;
-        return v[4] >= '2' && v[4] <= '8' ? v[4] - '0' : 4;
-    }();
-    // C rows and scratch rows take 16-byte stores: F % 8 == 0 covers fp16, fp32 and scratch
-    if (aligned && lean_ok && fifo_depth > 0 && a.n_peers == 0 && (((uintptr_t)a.C & 15) == 0) && a.F >= 64) {
-        dim3 rgrid(n_items, ceil_div(ceil_div(a.F, 64), 2));
-#define TRS_FIFO_LAUNCH(D)                                                                                        \
-    do {                                                                                                          \
-        constexpr int SM = 2 * (D * kFifoStage + kFifoIdBlocks * 512);                                            \
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_fifo<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM)); \
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_fifo<D, 2>, cudaFuncAttributePreferredSharedMemoryCarveout,   \
-                                      cudaSharedmemCarveoutMaxShared));                                           \
-        k_window_spmm_fifo<D, 2><<<rgrid, 64, SM, st>>>(a);                                                        \
-    } while (0)
-        if (fifo_depth <= 3) TRS_FIFO_LAUNCH(3);
-        else if (fifo_depth == 4) TRS_FIFO_LAUNCH(4);
-        else if (fifo_depth <= 6) TRS_FIFO_LAUNCH(6);
-        else TRS_FIFO_LAUNCH(8);
-#undef TRS_FIFO_LAUNCH
-        TRS_LAUNCH_CHECK();
-        return TRS_OK;
-    }
     if (aligned && lean_ok && use_lean) {
         static const int lean_stages = [] { const char* v = getenv("TRS_LEAN_STAGES"); return v && atoi(v) == 3 ? 3 : 4; }();
         if (lean_stages == 3) {
