@@ -455,6 +455,137 @@ def run_sddmm(args):
     print(json.dumps(line), flush=True)
 
 
+class _QuietStdout:
+    """The reference's CPU modules print tables; keep them out of this program's stdout."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        self.null = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(self.null, 1)
+
+    def __exit__(self, *a):
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+        os.close(self.null)
+
+
+def _row_sample(rp, col, val, r0, rows):
+    """CSR of rows [r0, r0 + rows) of the matrix (columns keep their ids), on the CPU."""
+    rp = rp.cpu()
+    r1 = min(r0 + rows, rp.numel() - 1)
+    e0, e1 = int(rp[r0]), int(rp[r1])
+    return (rp[r0:r1 + 1] - e0).contiguous(), col[e0:e1].cpu().contiguous(), val[e0:e1].cpu().contiguous(), e1 - e0
+
+
+def _bounded_cpu(fn, rp, col, val, budget_s=8.0, first_rows=1024):
+    """Times fn(sample) on row samples that start a third of the way into the matrix and double in
+    length until one run takes budget_s / 4 or the whole matrix is covered (the reference's CPU
+    builder is quadratic in the columns of a window, so the hub rows of an R-MAT graph, which sit at
+    ids with few set bits, are kept out of small samples).  Returns (seconds, entries, description)."""
+    n = rp.numel() - 1
+    rows = min(first_rows, n)
+    while True:
+        r0 = 0 if rows >= n else min((n // 3) // 16 * 16, (n - rows) // 16 * 16)
+        sample = _row_sample(rp, col, val, r0, rows)
+        with _QuietStdout():
+            t0 = time.perf_counter()
+            fn(*sample[:3])
+            sec = time.perf_counter() - t0
+        best = (sec, sample[3], f"rows [{r0}, {min(r0 + rows, n)}) of the workload: {sample[3]} entries, one run")
+        if sec >= budget_s / 4 or rows >= n:
+            return best
+        rows = min(n, rows * 2)
+
+
+def run_build(args):
+    """Format builder: CSR on the device -> the 29 arrays of the reference."""
+    from trspmm import build_format
+    dev = torch.device("cuda", 0)
+    rp, col, val, _ = make_matrix(args.workload, dev)
+    n, nnz = rp.numel() - 1, col.numel()
+    steps = max(1, min(args.steps, 10))
+    for _ in range(min(args.warmup, 3)):
+        fmt, st = build_format(rp, col, val)
+        del fmt
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clocks:
+        t0 = time.perf_counter()
+        kernel_ms = 0.0
+        for _ in range(steps):
+            fmt, st = build_format(rp, col, val)
+            kernel_ms += st["build_ms"]
+            out_bytes = sum(a.numel() * a.element_size() for a in fmt.arrays())
+            del fmt
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
+    peak, src = peaks()
+    alg = nnz * 12 + (n + 1) * 4 + out_bytes   # CSR in (i32 column, f32 value, row pointers... read once) + every array written once
+    line = {"metric": "format build M nnz/s", "value": nnz / (ms * 1e-3) / 1e6, "unit": "Mnnz/s", "n_gpus": 1,
+            "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "i32 / u8 / f32->f16", "data": "synthetic",
+            "config": {"workload": args.workload, "op": "build", "n_rows": n, "nnz": nnz,
+                       "call": "trs_build_create (wall time, includes its device allocations)",
+                       "device_ms_per_build": kernel_ms / steps, "output_bytes": out_bytes,
+                       "groups": st["groups"], "tiles": st["tiles"], "tc_blocks": st["tc_blocks"]},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None,
+                         "kernel": "kb_* pipeline (CUB sorts dominate)"},
+            "gpu_launches": None, "clocks": clocks.summary()}
+    if not args.no_cpu:
+        from oracle import oracle as O
+        have_ref = O.reference_module("Libra5BlockOnline") is not None
+        fn = (lambda a, b, c: O.reference_builder(a, b, c)) if have_ref else (lambda a, b, c: O.build_format(a, b, c))
+        sec, entries, what = _bounded_cpu(fn, rp, col, val)
+        line["cpu_baseline"] = {"value": entries / sec / 1e6, "unit": "Mnnz/s", "cores": 1,
+                                "kind": "reference" if have_ref else "port", "sample": what}
+    print(json.dumps(line), flush=True)
+
+
+def run_match24(args):
+    """2:4 matching statistics: the three deterministic variants on the GPU,
+    the reference's compiled CPU modules timed beside them on a bounded sample."""
+    from trspmm import match24
+    dev = torch.device("cuda", 0)
+    rp, col, val, _ = make_matrix(args.workload, dev)
+    n, nnz = rp.numel() - 1, col.numel()
+    peak, src = peaks()
+    ref_names = {"para_dr": ("matching_utils", "match_2to4"), "hash": ("matching_utils_hash", "match_2to4_hash"),
+                 "bucket": ("matching_utils_bucket", "match_2to4_bucket")}
+    out = {}
+    for variant in ("para_dr", "hash", "bucket"):
+        for _ in range(args.warmup):
+            match24.match_stats(variant, rp, col)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            match24.match_stats(variant, rp, col)   # synchronous: returns the statistics
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        alg = nnz * 4 + (n + 1) * 4
+        out[variant] = {"ms": ms, "Mnnz_per_s": nnz / (ms * 1e-3) / 1e6, "GBps": alg / (ms * 1e-3) / 1e9,
+                        "frac": alg / (ms * 1e-3) / 1e9 / peak}
+        if not args.no_cpu:
+            from oracle import oracle as O
+            mod = O.reference_module(ref_names[variant][0])
+            if mod is not None:
+                f = getattr(mod, ref_names[variant][1])
+                sec, entries, what = _bounded_cpu(lambda a, b, c: f(a.numpy(), b.numpy(), c.numpy()), rp, col, val, budget_s=4.0)
+                out[variant]["cpu_reference"] = {"Mnnz_per_s": entries / sec / 1e6, "cores": os.cpu_count(), "sample": what}
+    best = out["para_dr"]
+    line = {"metric": "2:4 matching statistics M nnz/s (para_dr variant)", "value": best["Mnnz_per_s"], "unit": "Mnnz/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True,
+            "dtype": "i32", "data": "synthetic",
+            "config": {"workload": args.workload, "op": "match24", "n_rows": n, "nnz": nnz, "variants": out,
+                       "call": "trs_match24_stats (synchronous; wall time)"},
+            "roofline": {"bound": "hbm", "achieved": best["GBps"], "peak": peak, "unit": "GB/s", "frac": best["frac"],
+                         "peak_source": src, "traffic": None, "kernel": "km_para_dr"},
+            "gpu_launches": None}
+    if "cpu_reference" in best:
+        line["cpu_baseline"] = {"value": best["cpu_reference"]["Mnnz_per_s"], "unit": "Mnnz/s", "cores": os.cpu_count(),
+                                "kind": "reference", "sample": best["cpu_reference"]["sample"]}
+    print(json.dumps(line), flush=True)
+
+
 def run_gcn(args, rank, world, local_rank):
     """Two-layer GCN forward (BASELINE config 4 shape): features 256 -> 128 -> 64, ReLU between."""
     import torch.distributed as dist
@@ -517,7 +648,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--reorder", default="none", choices=["none", "minhash", "hub", "degree"],
                     help="spmm: re-order the rows first (a separate, labelled configuration)")
-    ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn"],
+    ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn", "build", "match24"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
     ap.add_argument("--gather", default="h1", choices=["h1", "z2", "fused"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
@@ -532,6 +663,12 @@ def main():
             run_sddmm(args)
     elif args.op == "gcn":
         run_gcn(args, rank, world, local_rank)
+    elif args.op == "build":
+        if rank == 0:
+            run_build(args)
+    elif args.op == "match24":
+        if rank == 0:
+            run_match24(args)
     else:
         run_ours(args, rank, world, local_rank)
 
