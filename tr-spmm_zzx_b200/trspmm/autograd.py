@@ -4,7 +4,7 @@ The reference stops at the forward operator (spmm_forward_fp16_tcu_cuda_sptc_mma
 TR-source/SpMM/mGCN_online.cpp:760); it has no backward pass and no transpose.  For training
 the two adjoints are
     dB       = Aᵀ · dC                      -> the same fused SpMM over the format of Aᵀ
-    dval[e]  = < dC[row(e), :], B[col(e), :] >  -> SDDMM on A's pattern (trs_sddmm)
+    dval[e]  = < dC[row(e), :], B[col(e), :] >  -> planned SDDMM on A's pattern (trs_sddmm_plan_run)
 Both formats are built lossless (strict mode): the reference-compatible format drops the third and
 fourth non-zero of a row inside a 4-column group, and the dropped sets of A and Aᵀ differ, so the
 lossy pair would not be adjoint to each other.
@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from .builder import build_format
-from .sddmm import sddmm
+from .sddmm import SddmmPlan
 from .spmm import SpmmPlan
 
 
@@ -46,7 +46,7 @@ class _SpmmFn(torch.autograd.Function):
         dB = op.plan_t.run(dC, out_dtype=torch.float16) if ctx.needs_input_grad[2] else None
         dval = None
         if ctx.values_need_grad:
-            dval = sddmm(op.rowptr, op.col, dC, B.contiguous()).float()
+            dval = op.sddmm_plan().run(dC, B.contiguous()).float()
         return None, dval, dB
 
 
@@ -70,6 +70,14 @@ class DifferentiableSpmm:
         self.format_t, self.stats_t = build_format(rp_t.contiguous(), col_t.contiguous(), val_t.contiguous(),
                                                    **build_kwargs)
         self.plan_t = SpmmPlan(self.format_t, self.n_cols, self.n_rows)
+        self._sddmm_plan = None
+
+    def sddmm_plan(self) -> SddmmPlan:
+        """Planned SDDMM over A's pattern (built on first use: only callers that ask for the gradient
+        of the stored values need it)."""
+        if self._sddmm_plan is None:
+            self._sddmm_plan = SddmmPlan(self.rowptr, self.col, self.n_cols)
+        return self._sddmm_plan
 
     def __call__(self, B: torch.Tensor, values: torch.Tensor | None = None) -> torch.Tensor:
         if B.dtype != torch.float16 or B.dim() != 2 or B.shape[0] != self.n_cols:
