@@ -499,7 +499,7 @@ def _bounded_cpu(fn, rp, col, val, budget_s=8.0, first_rows=1024):
 
 
 def run_build(args):
-    """Format builder: CSR on the device -> the 29 arrays of the reference."""
+    """Format builder (block_sptc_2to4_online, block_online.cpp:545-871): CSR on the device -> the 29 arrays."""
     from trspmm import build_format
     dev = torch.device("cuda", 0)
     rp, col, val, _ = make_matrix(args.workload, dev)
@@ -543,7 +543,7 @@ def run_build(args):
 
 
 def run_match24(args):
-    """2:4 matching statistics: the three deterministic variants on the GPU,
+    """2:4 matching statistics (the reference's match_2to4* modules): the three deterministic variants on the GPU,
     the reference's compiled CPU modules timed beside them on a bounded sample."""
     from trspmm import match24
     dev = torch.device("cuda", 0)
