@@ -147,3 +147,19 @@ def test_even_row_split_covers_all_rows():
         assert per * w == padded and padded >= n and padded - n < w + per
         covered = sum(max(0, min((r + 1) * per, n) - r * per) for r in range(w))
         assert covered == n
+
+
+def test_rescale_costs_moves_windows_away_from_the_slow_rank():
+    from trspmm.shard import cuts_from_window_costs, rescale_costs
+    W, n = 400, 400 * 16
+    cost = torch.ones(W)
+    cuts = cuts_from_window_costs(cost, 4, n)
+    assert cuts == [0, 1600, 3200, 4800, 6400]
+    # rank 1 measured 50 % slower than the others: its range must shrink, the total stays covered
+    new_cost = rescale_costs(cost, cuts, [1.0, 1.5, 1.0, 1.0])
+    new_cuts = cuts_from_window_costs(new_cost, 4, n)
+    assert new_cuts[0] == 0 and new_cuts[-1] == n and all(b >= a for a, b in zip(new_cuts, new_cuts[1:]))
+    assert new_cuts[2] - new_cuts[1] < cuts[2] - cuts[1]
+    assert all(c % 16 == 0 for c in new_cuts)
+    # equal times change nothing
+    assert cuts_from_window_costs(rescale_costs(cost, cuts, [2.0] * 4), 4, n) == cuts

@@ -53,6 +53,21 @@ def cuts_from_window_costs(cost: torch.Tensor, parts: int, n_rows: int, window: 
     return cuts
 
 
+def rescale_costs(cost: torch.Tensor, cuts, times, window: int = 16, damping: float = 0.8):
+    """Per-window costs corrected by what the ranks measured: the windows of a rank that ran longer
+    than the mean get proportionally heavier (damped), so that the next cut moves windows away
+    from it.  `cuts` are the row boundaries the times were measured with."""
+    cost = cost.clone()
+    mean = sum(times) / len(times)
+    if mean <= 0:
+        return cost
+    for r, t in enumerate(times):
+        w0, w1 = cuts[r] // window, (cuts[r + 1] + window - 1) // window
+        if w1 > w0 and t > 0:
+            cost[w0:w1] *= (t / mean) ** damping
+    return cost
+
+
 def window_steps(fmt, n_windows: int):
     """k-steps per window of a built format: packed tiles + pairs of TC blocks."""
     off = fmt.s_window_tile_offset
