@@ -116,38 +116,43 @@ __global__ void km_para_dr(WinCols wc, Work wk, int W, int n_rows, int window, i
     if (n == 0) return;
     const int win_rows = min(window, n_rows - w * window);
     const unsigned short* m = wc.mask + b;
-    unsigned char* matched = wk.matched + b;
     unsigned short *G1 = wk.pG1 + b, *G2 = wk.pG2 + b;
     unsigned char *n1 = wk.pn1 + b, *n2 = wk.pn2 + b, *used = wk.pused + b, *pool = wk.pool + b;
-    for (int i = lane; i < n; i += 32) { matched[i] = 0; used[i] = 0; }
+    for (int i = lane; i < n; i += 32) used[i] = 0;
     __syncwarp();
     int np = 0, nd = 0, fine = 0, coarse = 0, groups = 0;
     long long fake = 0;
-    // fine step (block_matching_window_para_dr.cpp:126-158)
+    // fine step (block_matching_window_para_dr.cpp:126-158).  A column can only be matched by one
+    // of the 32 columns before it, so the matched flags of the columns ahead are a 32-bit window
+    // kept in a register (bit k = column i + 1 + k), identical in every lane: the serial loop then
+    // reads only the read-only masks from memory.
+    unsigned ahead = 0u;
+    bool cur = false;  // column i is matched
     for (int i = 0; i < n; ++i) {
-        if (matched[i]) continue;
-        const unsigned mi = m[i];
-        const int j_end = min(i + 1 + 32, n);
-        const int j = i + 1 + lane;
-        const bool ok = j < j_end && !matched[j];
-        const int cost = ok ? __popc(mi & m[j]) : 99;
-        const int pick = pick_partner(ok, cost, t_max, lane);
-        if (lane == 0) {
-            matched[i] = 1;
-            if (pick >= 0) {
-                const int bj = i + 1 + pick;
-                matched[bj] = 1;
-                G1[np] = (unsigned short)(mi & m[bj]);
-                G2[np] = (unsigned short)(mi | m[bj]);
-                n1[np] = (unsigned char)__popc(mi);
-                n2[np] = (unsigned char)__popc((unsigned)m[bj]);
-            } else {
-                pool[nd] = (unsigned char)__popc(mi);
+        if (!cur) {
+            const unsigned mi = m[i];
+            const int j_end = min(i + 1 + 32, n);
+            const int j = i + 1 + lane;
+            const bool ok = j < j_end && !((ahead >> lane) & 1u);
+            const int cost = ok ? __popc(mi & m[j]) : 99;
+            const int pick = pick_partner(ok, cost, t_max, lane);
+            if (lane == 0) {
+                if (pick >= 0) {
+                    const int bj = i + 1 + pick;
+                    G1[np] = (unsigned short)(mi & m[bj]);
+                    G2[np] = (unsigned short)(mi | m[bj]);
+                    n1[np] = (unsigned char)__popc(mi);
+                    n2[np] = (unsigned char)__popc((unsigned)m[bj]);
+                } else {
+                    pool[nd] = (unsigned char)__popc(mi);
+                }
             }
+            if (pick >= 0) { ahead |= 1u << pick; ++np; } else { ++nd; ++fine; }
         }
-        if (pick >= 0) ++np; else { ++nd; ++fine; }
-        __syncwarp();
+        cur = ahead & 1u;
+        ahead >>= 1;
     }
+    __syncwarp();
     // coarse step (:169-204)
     group_pairs(np, 1024, 1, G1, G2, used, lane,
                 [&](int i, int j) { fake += 2 * win_rows - ((int)n1[i] + n2[i] + n1[j] + n2[j]); ++groups; },
