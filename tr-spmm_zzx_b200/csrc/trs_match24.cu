@@ -209,18 +209,31 @@ __global__ void km_hash(WinCols wc, Work wk, int W, int n_rows, int window, MSta
     __syncwarp();
     int np = 0, fine = 0, coarse = 0, groups = 0;
     long long fake = 0;
-    // phase 1 (block_matching_hash.cpp:142-163): serial by nature, lane 0 walks the chains
+    // phase 1 (block_matching_hash.cpp:142-163).  The lookups only depend on the masks, so the
+    // whole warp resolves them first, in parallel: run_lo[i] = sorted position where the run of
+    // column i's complement mask starts (-1: no such run), and top[start of a run] = its last
+    // position.  The chain walk itself is serial by nature and stays with lane 0, now without any
+    // binary search on its critical path.
+    int* run_lo = wk.idx_c + b;
+    auto lower = [&](unsigned key) {  // first sorted position whose mask is >= key
+        int lo = 0, hi = n;
+        while (lo < hi) { const int mid = (lo + hi) >> 1; if (m[by_mask[mid]] < key) lo = mid + 1; else hi = mid; }
+        return lo;
+    };
+    for (int i = lane; i < n; i += 32) {
+        const unsigned ideal = (~(unsigned)m[i]) & 0xFFFFu;
+        const int lo = lower(ideal);
+        run_lo[i] = (lo < n && m[by_mask[lo]] == ideal) ? lo : -1;
+        const unsigned mq = m[by_mask[i]];   // i as a sorted position: is it the last of its run?
+        if (i == n - 1 || m[by_mask[i + 1]] != mq) top[lower(mq)] = i;
+    }
+    __syncwarp();
     if (lane == 0) {
         for (int i = 0; i < n; ++i) {
             if (matched[i]) continue;
-            const unsigned ideal = (~(unsigned)m[i]) & 0xFFFFu;
-            // run of `ideal` in by_mask: [lo, hi)
-            int lo = 0, hi = n;
-            while (lo < hi) { const int mid = (lo + hi) >> 1; if (m[by_mask[mid]] < ideal) lo = mid + 1; else hi = mid; }
-            if (lo >= n || m[by_mask[lo]] != ideal) continue;
-            int e = lo, h2 = n;
-            while (e < h2) { const int mid = (e + h2) >> 1; if (m[by_mask[mid]] <= ideal) e = mid + 1; else h2 = mid; }
-            int p = top[lo] == -2 ? e - 1 : top[lo];   // highest not yet discarded position of the run
+            const int lo = run_lo[i];
+            if (lo < 0) continue;
+            int p = top[lo];   // highest not yet discarded position of the run
             while (p >= lo && matched[by_mask[p]]) --p;
             top[lo] = p;
             if (p < lo) continue;
@@ -232,31 +245,43 @@ __global__ void km_hash(WinCols wc, Work wk, int W, int n_rows, int window, MSta
     }
     np = __shfl_sync(0xffffffffu, np, 0);
     __syncwarp();
-    // phase 2 (:170-221)
+    // phase 2 (:170-221).  Phase 1 is over, so its matched flags are read-only now; the flags of the
+    // 32 columns ahead sit in a register window (bit k = column i + 1 + k), refilled from the array
+    // 32 positions at a time, and the matches of this phase are recorded in the window only.
+    unsigned ahead = __ballot_sync(0xffffffffu, 1 + lane < n && matched[1 + lane]);
+    int fbase = 33;
+    unsigned feed = __ballot_sync(0xffffffffu, fbase + lane < n && matched[fbase + lane]);
+    bool cur = matched[0] != 0;
     for (int i = 0; i < n; ++i) {
-        if (matched[i]) continue;
-        const unsigned mi = m[i];
-        const int j_end = min(i + 1 + 32, n);
-        const int j = i + 1 + lane;
-        const bool ok = j < j_end && !matched[j];
-        const int cost = ok ? __popc(mi & m[j]) : 99;
-        const int pick = pick_partner(ok, cost, 8, lane);
-        if (lane == 0) {
-            matched[i] = 1;
-            if (pick >= 0) {
-                const int bj = i + 1 + pick;
-                matched[bj] = 1;
-                G1[np] = (unsigned short)(mi & m[bj]);
-                G2[np] = (unsigned short)(mi | m[bj]);
-                n1[np] = (unsigned char)(__popc(mi) + __popc((unsigned)m[bj]));
-            } else {
-                G1[np] = 0; G2[np] = (unsigned short)mi; n1[np] = (unsigned char)__popc(mi);
+        if (!cur) {
+            const unsigned mi = m[i];
+            const int j_end = min(i + 1 + 32, n);
+            const int j = i + 1 + lane;
+            const bool ok = j < j_end && !((ahead >> lane) & 1u);
+            const int cost = ok ? __popc(mi & m[j]) : 99;
+            const int pick = pick_partner(ok, cost, 8, lane);
+            if (lane == 0) {
+                if (pick >= 0) {
+                    const int bj = i + 1 + pick;
+                    G1[np] = (unsigned short)(mi & m[bj]);
+                    G2[np] = (unsigned short)(mi | m[bj]);
+                    n1[np] = (unsigned char)(__popc(mi) + __popc((unsigned)m[bj]));
+                } else {
+                    G1[np] = 0; G2[np] = (unsigned short)mi; n1[np] = (unsigned char)__popc(mi);
+                }
             }
+            if (pick >= 0) ahead |= 1u << pick; else ++fine;
+            ++np;
         }
-        if (pick < 0) ++fine;
-        ++np;
-        __syncwarp();
+        const int nx = i + 33;   // the column that enters the window
+        if (nx - fbase == 32) {
+            fbase += 32;
+            feed = __ballot_sync(0xffffffffu, fbase + lane < n && matched[fbase + lane]);
+        }
+        cur = ahead & 1u;
+        ahead = (ahead >> 1) | (((feed >> (nx - fbase)) & 1u) << 31);
     }
+    __syncwarp();
     // coarse step (:227-277)
     group_pairs(np, 1024, 1, G1, G2, used, lane,
                 [&](int i, int j) { fake += 2 * win_rows - ((int)n1[i] + n1[j]); ++groups; },
