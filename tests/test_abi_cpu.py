@@ -45,6 +45,16 @@ def test_entry_points_reject_bad_arguments_without_a_device():
     assert lib.trs_spmm_plan_create(ctypes.byref(fmt), 16, 16, 17, 1, None, ctypes.byref(plan)) == -2
     assert lib.trs_spmm_run(None, None, None, 8, 0, None, 0, None) == -1
     assert lib.trs_sddmm(None, None, None, None, None, 4, 4, 8, None) == -1
+    # entries added beside the reference's surface: same convention (negative code, nothing launched)
+    assert lib.trs_spmm_run_windows(None, None, None, 8, 0, 0, None, 0, None, 0, 1) == -1
+    assert lib.trs_spmm_num_windows(None) == -1
+    assert lib.trs_resident_submit(None, None, None, 8, 0) == -1
+    assert lib.trs_resident_wait(None) == -1
+    sp = ctypes.c_void_p()
+    assert lib.trs_sddmm_plan_create(None, None, 4, 4, None, ctypes.byref(sp)) == -1
+    assert lib.trs_sddmm_plan_create(rp0 := (ctypes.c_int * 2)(0, 0), None, 0, 4, None, ctypes.byref(sp)) == -1
+    assert lib.trs_sddmm_plan_run(None, None, None, None, 64, None) == -1
+    assert lib.trs_sddmm_plan_destroy(None) == 0
     cfg = _lib.TrsBuildConfig(32, 32, 3, 8, 99, 0.0, 0, 2, 0)
     b = ctypes.c_void_p()
     rp = (ctypes.c_int * 2)(0, 0)
