@@ -273,7 +273,8 @@ int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, cons
  * and the dot products run on the tensor cores (mma m16n8k16, fp32 accumulate) for K = 32, 64,
  * 128 with 16-byte aligned X / Y; other shapes run the entry-parallel kernel of trs_sddmm.  The
  * pattern must be canonical CSR (columns ascending and unique inside a row) and stay valid and
- * unchanged while the plan lives.  Results equal trs_sddmm's up to fp32 summation order.
+ * unchanged while the plan lives (checked at creation: TRS_E_COLUMN for a column outside
+ * [0, n_cols), TRS_E_NOT_CANONICAL otherwise).  Results equal trs_sddmm's up to fp32 summation order.
  * No counterpart in the reference. */
 typedef struct trs_sddmm_plan trs_sddmm_plan;
 int trs_sddmm_plan_create(const int32_t* rowptr, const int32_t* col, int n_rows, int n_cols,

@@ -96,3 +96,21 @@ def test_planned_sddmm_rectangular_empty_rows_and_empty_pattern():
     assert plan.n_pairs == torch.unique((r // 16) * 500 + col.long()).numel()
     empty = SddmmPlan(torch.zeros(301, dtype=torch.int32).cuda(), torch.zeros(0, dtype=torch.int32).cuda(), 500)
     assert empty.n_blocks == 0 and empty.run(X.cuda(), Y.cuda()).numel() == 0
+
+
+def test_sddmm_plan_rejects_patterns_it_cannot_address():
+    """The plan finds an entry as start + popcount, which needs ascending unique columns per row."""
+    from trspmm import SddmmPlan
+    from trspmm._lib import TrsError
+    rp = torch.tensor([0, 3, 5], dtype=torch.int32).cuda()
+    with pytest.raises(TrsError) as e:
+        SddmmPlan(rp, torch.tensor([0, 2, 1, 0, 3], dtype=torch.int32).cuda(), 4)      # 2, 1 descending in row 0
+    assert e.value.code == -8
+    with pytest.raises(TrsError) as e:
+        SddmmPlan(rp, torch.tensor([0, 1, 1, 0, 3], dtype=torch.int32).cuda(), 4)      # duplicate column
+    assert e.value.code == -8
+    with pytest.raises(TrsError) as e:
+        SddmmPlan(rp, torch.tensor([0, 1, 2, 0, 4], dtype=torch.int32).cuda(), 4)      # column 4 of 4
+    assert e.value.code == -5
+    ok = SddmmPlan(rp, torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32).cuda(), 4)
+    assert ok.n_pairs == 4   # columns 0, 1, 2, 3 of the single window (column 0 twice)

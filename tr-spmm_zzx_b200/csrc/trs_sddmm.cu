@@ -150,11 +150,17 @@ __device__ __forceinline__ int row_of_entry(const int* __restrict__ rowptr, int 
     return lo;
 }
 
-__global__ void ksp_keys(const int* __restrict__ rowptr, const int* __restrict__ col, int n_rows, long long nnz,
-                         unsigned long long* __restrict__ key, int* __restrict__ ent) {
+// Also validates the pattern: err |= 1 for a column outside [0, n_cols), |= 2 for columns that are
+// not strictly ascending inside a row (the plan's entry addressing relies on canonical CSR).
+__global__ void ksp_keys(const int* __restrict__ rowptr, const int* __restrict__ col, int n_rows, int n_cols,
+                         long long nnz, unsigned long long* __restrict__ key, int* __restrict__ ent,
+                         int* __restrict__ err) {
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= nnz) return;
     const int r = row_of_entry(rowptr, n_rows, e);
+    const int c = col[e];
+    if (c < 0 || c >= n_cols) { atomicOr(err, 1); return; }
+    if (e > (long long)rowptr[r] && col[e - 1] >= c) atomicOr(err, 2);
     key[e] = ((unsigned long long)(r >> 4) << 32) | (unsigned)col[e];
     ent[e] = (int)e;
 }
@@ -348,7 +354,20 @@ extern "C" int trs_sddmm_plan_create(const int32_t* rowptr, const int32_t* col, 
     if (!rc) rc = blk_off.alloc((size_t)W + 1);
     if (rc) return fail(rc);
     auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
-    ksp_keys<<<grid(nnz), 256, 0, st>>>(rowptr, col, n_rows, nnz, key_a.p, ent_a.p);
+    DevBuf<int> d_err;
+    rc = d_err.alloc(1);
+    if (rc) return fail(rc);
+    cudaMemsetAsync(d_err.p, 0, sizeof(int), st);
+    ksp_keys<<<grid(nnz), 256, 0, st>>>(rowptr, col, n_rows, n_cols, nnz, key_a.p, ent_a.p, d_err.p);
+    {
+        int herr = 0;
+        cudaError_t ee = cudaMemcpyAsync(&herr, d_err.p, sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (ee == cudaSuccess) ee = cudaStreamSynchronize(st);
+        d_err.release();
+        if (ee != cudaSuccess) return fail((int)ee);
+        if (herr & 1) return fail(TRS_E_COLUMN);
+        if (herr & 2) return fail(TRS_E_NOT_CANONICAL);
+    }
     int wbits = 1;
     while ((1ll << wbits) < W) ++wbits;
     cub::DoubleBuffer<unsigned long long> kb(key_a.p, key_b.p);
