@@ -468,7 +468,8 @@ struct LeanTile {
     static constexpr int ROWB = FS * 2 + 16;
     static constexpr int BBYTES = 16 * ROWB;
     static constexpr int STAGE = BBYTES + 512;
-    static constexpr int SMEM = STAGE * STAGES + kIdxRing * 64;
+    static constexpr int RING = STAGES <= 4 ? 8 : 16;   // id ring slots: a power of two above 2 * STAGES - 2
+    static constexpr int SMEM = STAGE * STAGES + RING * 64;
     static constexpr int THREADS = WARPS * 32;
     static constexpr int CPR = FS / 8;
 };
@@ -477,7 +478,7 @@ template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArgs a) {
     using T = LeanTile<WARPS, STAGES>;
     constexpr int kStages = STAGES;                 // shadows the file-wide stage count
-    constexpr int kIdxAhead = 2 * STAGES - 2;       // column ids are fetched this many steps ahead (ring of 8)
+    constexpr int kIdxAhead = 2 * STAGES - 2;       // column ids are fetched this many steps ahead (ring of T::RING)
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -512,19 +513,19 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArg
     auto issue_idx = [&](int m) {
         if (tid < 4 && m < nsteps) {
             const int s = it.step_begin + m;
-            const uint32_t dst = ring0 + (m & (kIdxRing - 1)) * 64 + tid * 16;
+            const uint32_t dst = ring0 + (m & (T::RING - 1)) * 64 + tid * 16;
             if (s < it.ntiles) {
                 cp_async16(dst, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + tid * 4, 16);
             } else {
                 const int b = it.blk0 + 2 * (s - it.ntiles) + (tid >> 1);
                 if (b < it.blk_end) cp_async16(dst, a.f.t_column + (size_t)b * 8 + (tid & 1) * 4, 16);
-                else *(int4*)(smem + T::STAGE * kStages + (m & (kIdxRing - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
+                else *(int4*)(smem + T::STAGE * kStages + (m & (T::RING - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
             }
         }
     };
 
     auto issue = [&](int j, int stage) {
-        const int* cols = ring + (j & (kIdxRing - 1)) * 16;
+        const int* cols = ring + (j & (T::RING - 1)) * 16;
         const int c0 = cols[row0], c1 = cols[row0 + 8];
         const uint32_t o0 = (uint32_t)max(c0, 0) * pitch16 + chunk16;
         const uint32_t o1 = (uint32_t)max(c1, 0) * pitch16 + chunk16;
@@ -1434,7 +1435,10 @@ static int launch_window_kernel(const KernelArgs& a, int n_items, bool lean_ok, 
     dim3 grid(n_items, ceil_div(a.F, T::FS));
     static const bool use_lean = [] { const char* v = getenv("TRS_SPMM_KERNEL"); return !(v && strcmp(v, "cpasync_v1") == 0); }();
     if (aligned && lean_ok && use_lean) {
-        static const int lean_stages = [] { const char* v = getenv("TRS_LEAN_STAGES"); return v && atoi(v) == 3 ? 3 : 4; }();
+        // Three stages are the default: measured 1-2 % faster than four at R-MAT scale 21 (3.18 vs 3.23 ms,
+        // 3.24 vs 3.28 ms on two boxes) and equal on the clustered case; five stages (8 CTAs per SM) and
+        // 2-warp CTAs with the feature slabs on gridDim.y were slower (3.50 and 3.67 ms).
+        static const int lean_stages = [] { const char* v = getenv("TRS_LEAN_STAGES"); return v && atoi(v) == 4 ? 4 : 3; }();
         if (lean_stages == 3) {
             using L = LeanTile<WARPS, 3>;
             TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
