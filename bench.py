@@ -40,6 +40,7 @@ sys.path.insert(0, str(ROOT))
 import torch  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
+LEG_NAMES = ("h2d_ms", "allgather_ms", "kernel_ms", "d2h_ms")
 
 WORKLOADS = {
     # name: (generator, kwargs, F)
@@ -155,6 +156,47 @@ def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):
     return nnz * 6 + (n_rows + 1) * 4 + n_cols * F * 2 + n_rows * F * out_bytes
 
 
+def dropped_rows(fmt):
+    """Local rows that lost an entry to the reference builder's 2-per-group rule
+    (block_online.cpp:683-695): a mask bit without a stored slot."""
+    if fmt.s_mask.numel() == 0:
+        return torch.zeros(0, dtype=torch.int64, device=fmt.device)
+    m = fmt.s_mask.to(torch.int32)
+    bits = (m & 1) + ((m >> 1) & 1) + ((m >> 2) & 1) + ((m >> 3) & 1)          # [G, 16]
+    slots = (fmt.s_pos >= 0).sum(-1).to(torch.int32)                            # [G, 16]
+    g, r = torch.nonzero(bits > slots, as_tuple=True)
+    return torch.unique(fmt.s_window[g].long() * 16 + r)
+
+
+def parity_sample(rp_l, col_l, val_l, fmt, B, out, n_sample=4096, seed=123):
+    """Checker run after the timed region, on every rank: `n_sample` of this rank's own rows that
+    lost no entry, recomputed as a CSR product in fp32 by torch.sparse on the GPU (fp16-rounded
+    values and B, like the kernel's inputs) and compared with the rows the kernel wrote.
+    Returns (max relative error, mean relative error, rows checked); the relative error of an
+    element is |x - y| / max(|y|, 1e-3 * largest |y| of its row)."""
+    dev = out.device
+    m = rp_l.numel() - 1
+    good = torch.ones(m, dtype=torch.bool, device=dev)
+    bad = dropped_rows(fmt)
+    good[bad[bad < m]] = False
+    pool = torch.nonzero(good).flatten()
+    if pool.numel() == 0:
+        return 0.0, 0.0, 0
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rows = pool[torch.randint(0, pool.numel(), (min(n_sample, pool.numel()),), device=dev, generator=g)]
+    rows = torch.unique(rows)
+    cnt = (rp_l[1:] - rp_l[:-1]).long()[rows]
+    sub_rp = torch.zeros(rows.numel() + 1, dtype=torch.int64, device=dev)
+    sub_rp[1:] = torch.cumsum(cnt, 0)
+    ent = torch.repeat_interleave(rp_l.long()[rows] - sub_rp[:-1], cnt) + torch.arange(int(sub_rp[-1]), device=dev)
+    A = torch.sparse_csr_tensor(sub_rp, col_l.long()[ent], val_l[ent].half().float(), (rows.numel(), B.shape[0]))
+    ref = torch.sparse.mm(A, B.float())
+    got = out[rows].float()
+    scale = torch.maximum(ref.abs(), 1e-3 * ref.abs().amax(dim=1, keepdim=True)).clamp_min(1e-30)
+    rel = (got - ref).abs() / scale
+    return float(rel.max()), float(rel.mean()), int(rows.numel())
+
+
 def cpu_spmm_time(rp, col, val, B, reps):
     """torch.sparse CSR fp32 matmul on all host threads; median seconds of `reps` runs after 1 warm-up."""
     from oracle import oracle as O
@@ -233,8 +275,10 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa_node = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        numa_node = shard.bind_to_gpu_numa_node(local_rank)   # host buffers of this rank local to its GPU
 
     rp, col, val, F = make_matrix(args.workload, dev)
     n = rp.numel() - 1
@@ -253,7 +297,7 @@ def run_ours(args, rank, world, local_rank):
         # first cut by nnz; then re-cut by the k-steps the built format really has per window
         # (hub windows share columns, so their cost per nnz is lower) and build again
         (r0, r1), (rp_l, col_l, val_l) = shard.shard_for_rank(rp, col, val, rank, world)
-        fmt, st = build_format(rp_l, col_l, val_l)
+        fmt, st = build_format(rp_l, col_l, val_l, strict=args.strict)
         W = (n + 15) // 16
         cost = torch.zeros(W, device=dev)
         w0 = r0 // 16
@@ -268,7 +312,7 @@ def run_ours(args, rank, world, local_rank):
         # step count): time the rank's own kernel, make the slow ranks' windows heavier, cut again
         Bt = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
         for _ in range(2):
-            fmt_t, _st = build_format(rp_l, col_l, val_l)
+            fmt_t, _st = build_format(rp_l, col_l, val_l, strict=args.strict)
             plan_t = SpmmPlan(fmt_t, max(r1 - r0, 1), n, validate=False)
             out_t = torch.empty((max(r1 - r0, 1), F), dtype=torch.float16, device=dev)
             for _i in range(3):
@@ -296,12 +340,13 @@ def run_ours(args, rank, world, local_rank):
     else:
         r0, r1, rp_l, col_l, val_l = 0, n, rp, col, val
     m_local = r1 - r0
-    fmt, st = build_format(rp_l, col_l, val_l)
+    fmt, st = build_format(rp_l, col_l, val_l, strict=args.strict)
     kept_local = st["nnz"] - st["dropped_nnz"]
     B = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
     plan = SpmmPlan(fmt, max(m_local, 1), n, validate=True)
     out = torch.empty((max(m_local, 1), F), dtype=torch.float16, device=dev)
     cpu_inputs = (rp.cpu(), col.cpu(), val.cpu()) if (world == 1 and not args.no_cpu) else None
+    rp_l, col_l, val_l = rp_l.clone(), col_l.clone(), val_l.clone()   # this rank's rows, kept for the parity sample
     del rp, col, val
     torch.cuda.empty_cache()
 
@@ -324,10 +369,15 @@ def run_ours(args, rank, world, local_rank):
         clocks.top_up(lambda: plan.run(B, out=out), torch.cuda.synchronize)
     ms = e0.elapsed_time(e1) / args.steps
     status = plan.status()
+    # ---- oracle inside the run: sampled rows of this rank against a CSR product of the same rows
+    p_max, p_mean, p_rows = parity_sample(rp_l, col_l, val_l, fmt, B, out)
+    del rp_l, col_l, val_l
+    torch.cuda.empty_cache()
 
     # ---- e2e with HOST buffers: B from pinned host memory, C back to the host, every step
     e2e_steps = max(2, min(args.steps, 8))
     h2d = d2h = 0.0
+    legs = {k: 0.0 for k in LEG_NAMES}
     if world == 1:
         # the host-buffer C-ABI entries of one GPU
         res = ResidentSpmm(fmt, max(m_local, 1), n, 16, F)
@@ -380,20 +430,29 @@ def run_ours(args, rank, world, local_rank):
             sh.submit(B_hosts[i & 1], C_hosts[i & 1])
         sh.wait()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        legs = sh.leg_ms()
         e2e_call = (f"ShardedHostSpmm.submit x steps + wait: each rank copies 1/{world} of B host->device, NCCL "
                     "all-gather over NVLink, own windows, own rows of C device->host; steps overlap on four streams")
         e2e_block_call = "ShardedHostSpmm.submit + wait per step"
     if not torch.equal(C_hosts[0], C_hosts[1]) or not torch.equal(C_hosts[0], out.cpu()):
         raise RuntimeError("host-buffer calls disagree with the device-resident result")
 
-    kept = torch.tensor([float(kept_local), ms, e2e_ms, e2e_sync_ms], device=dev, dtype=torch.float64)
+    kept = torch.tensor([float(kept_local), ms, e2e_ms, e2e_sync_ms, p_max, p_mean, float(p_rows)], device=dev,
+                        dtype=torch.float64)
     if world > 1:
         tot = kept.clone()
         dist.all_reduce(tot[0:1], op=dist.ReduceOp.SUM)
-        dist.all_reduce(tot[1:4], op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot[1:6], op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot[6:7], op=dist.ReduceOp.SUM)
         kept_total, ms, e2e_ms, e2e_sync_ms = float(tot[0]), float(tot[1]), float(tot[2]), float(tot[3])
+        p_max, p_mean, p_rows = float(tot[4]), float(tot[5]), int(tot[6])
+        legs_t = torch.tensor([legs[k] for k in LEG_NAMES], device=dev, dtype=torch.float64)
+        dist.all_reduce(legs_t, op=dist.ReduceOp.MAX)
+        legs = {k: float(v) for k, v in zip(LEG_NAMES, legs_t)}
     else:
         kept_total = float(kept_local)
+    if p_max > 1e-2 or p_mean > 1e-3:
+        raise RuntimeError(f"parity sample failed: max rel {p_max}, mean rel {p_mean} (bars 1e-2 / 1e-3)")
 
     if rank == 0:
         peak, peak_src = peaks()
@@ -406,7 +465,10 @@ def run_ours(args, rank, world, local_rank):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 in / f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": args.workload + ("" if reorder_note is None else "+rows:" + args.reorder),
+            "config": {"workload": args.workload + ("" if reorder_note is None else "+rows:" + args.reorder)
+                       + ("+strict" if args.strict else ""),
+                       "format": "lossless (strict): the entries the reference's builder drops ride the CUDA-core route"
+                                 if args.strict else "reference-compatible (drops reproduced)",
                        "reorder": reorder_note, "description": DESCRIPTIONS[args.workload], "n_rows": n,
                        "nnz": nnz_total, "kept_nnz": int(kept_total), "F": F, "out": "f16",
                        "parallelism": f"row-window shards x{world} balanced by k-steps and measured kernel time, B replicated, no collective",
@@ -415,17 +477,26 @@ def run_ours(args, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "algorithmic_bytes_per_step_rank0": alg_rank,
                          "algorithmic_bytes_per_step_job": alg_job,
-                         "traffic": MEASURED_TRAFFIC.get((args.workload, F)) if (world == 1 and reorder_note is None) else None,
+                         "traffic": MEASURED_TRAFFIC.get((args.workload, F)) if (world == 1 and reorder_note is None
+                                                                                  and not args.strict) else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch (profiles/)",
-                         "kernel": "k_window_spmm_lean"},
+                         "kernel": "k_window_spmm_warp"},
             "e2e": {"value": 2.0 * kept_total * F / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": n * F * 2, "d2h_bytes_per_step": n * F * 2,
-                    "h2d_ms": h2d / e2e_steps, "d2h_ms": d2h / e2e_steps, "steps": e2e_steps,
+                    "h2d_ms": h2d / e2e_steps if world == 1 else legs["h2d_ms"],
+                    "d2h_ms": d2h / e2e_steps if world == 1 else legs["d2h_ms"],
+                    "allgather_ms": legs["allgather_ms"], "kernel_ms": legs["kernel_ms"] if world > 1 else ms,
+                    "legs": "device time of each leg of the last streamed call, max over ranks" if world > 1 else
+                            "copy legs of the blocking calls (trs_timing)",
+                    "steps": e2e_steps, "numa_node_rank0": numa_node,
                     "call": e2e_call,
                     "blocking_call": {"value": 2.0 * kept_total * F / (e2e_sync_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                                       "ms_per_step": e2e_sync_ms, "call": e2e_block_call}},
             "gpu_launches": plan.launches * args.steps,
             "clocks": clocks.summary(), "kernel_status": status,
+            "parity_sample": {"max_rel": p_max, "mean_rel": p_mean, "rows": p_rows, "bars": [1e-2, 1e-3],
+                              "checker": "torch.sparse CSR fp32 product of sampled rows without dropped entries, on every "
+                                         "rank's own rows, worst rank reported"},
         }
         if cpu_inputs is not None:
             reps = 3
@@ -691,6 +762,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--reorder", default="none", choices=["none", "minhash", "hub", "degree"],
                     help="spmm: re-order the rows first (a separate, labelled configuration)")
+    ap.add_argument("--strict", action="store_true",
+                    help="spmm: lossless format (no dropped entries; value counts all nnz) - a separate, labelled configuration")
     ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn", "build", "match24"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
     ap.add_argument("--gather", default="h1", choices=["h1", "z2", "fused"], help="gcn: which matrix the ranks exchange")

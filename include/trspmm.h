@@ -265,7 +265,11 @@ int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, in
                       int dense_threshold, int t_max, void* stream, trs_match_stats* out);
 
 /* ---- SDDMM (no counterpart in the reference; defined by BASELINE config 3) -----------------
- * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e. */
+ * out[e] = fp16( sum_k fp32(X[row(e),k]) * fp32(Y[col(e),k]) ) for every CSR entry e.
+ * The call reads rowptr[0] and rowptr[n_rows] back to the host first (one stream synchronise per
+ * call; TRS_E_OFFSETS when they are not 0 / non-negative), then launches on `stream`.  The pattern
+ * is not validated beyond that: the kernel never reads outside X, Y or rowptr, and an entry whose
+ * column lies outside [0, n_cols) comes back as NaN.  Use the plan below for a checked pattern. */
 int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_half* X, const trs_half* Y,
               trs_half* out, int n_rows, int n_cols, int K, void* stream);
 /* Planned SDDMM for a pattern that is used many times (training epochs): the plan groups the

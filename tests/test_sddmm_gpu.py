@@ -114,3 +114,22 @@ def test_sddmm_plan_rejects_patterns_it_cannot_address():
     assert e.value.code == -5
     ok = SddmmPlan(rp, torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32).cuda(), 4)
     assert ok.n_pairs == 4   # columns 0, 1, 2, 3 of the single window (column 0 twice)
+
+
+def test_unplanned_entry_bounds_bad_columns():
+    """trs_sddmm does not validate the pattern; an out-of-range column must not become an
+    out-of-range gather: that entry comes back as NaN, every other entry is computed as usual."""
+    rp, col, _ = graphs.uniform_graph(512, 6, seed=1)
+    n = rp.numel() - 1
+    g = torch.Generator().manual_seed(0)
+    for K in (64, 40):
+        X = torch.randn(n, K, generator=g).half().cuda()
+        Y = torch.randn(n, K, generator=g).half().cuda()
+        good = sddmm(rp.cuda(), col.cuda(), X, Y)
+        bad_col = col.clone()
+        bad_col[5] = n + 1000
+        bad_col[77] = -3
+        out = sddmm(rp.cuda(), bad_col.cuda(), X, Y)
+        nan = torch.isnan(out)
+        assert nan.nonzero().flatten().tolist() == [5, 77]
+        assert torch.equal(out[~nan], good[~nan])

@@ -160,6 +160,23 @@ def test_spmm_rejects_bad_arrays():
     with pytest.raises(TrsError) as e:
         SpmmPlan(Format(named).to("cuda"), n, n, window=17)
     assert e.value.code == -2
+    # a TC bitmap that names more values than the block owns would read past t_value
+    assert named["t_binary"].numel() > 0
+    bad = dict(named); bad["t_binary"] = named["t_binary"].clone(); bad["t_binary"][0] ^= 1
+    with pytest.raises(TrsError) as e:
+        SpmmPlan(Format(bad).to("cuda"), n, n)
+    assert e.value.code == -4
+    # array lengths that disagree are refused before anything is handed to the library
+    bad = dict(named); bad["t_column"] = named["t_column"][:-8]
+    with pytest.raises(ValueError):
+        SpmmPlan(Format(bad).to("cuda"), n, n)
+    plan = SpmmPlan(Format(named).to("cuda"), n, n)
+    short_B = torch.zeros(n - 1, 32, dtype=torch.float16, device="cuda")
+    out = torch.empty(n, 32, device="cuda")
+    for call in (lambda: plan.run(short_B), lambda: plan.run_static(short_B, out),
+                 lambda: plan.run_windows(short_B, out, 0, 1), lambda: plan.run_bcast(short_B, [out.data_ptr()], 0)):
+        with pytest.raises(ValueError):
+            call()
 
 
 def test_ragged_last_window_and_empty_rows():
@@ -178,39 +195,76 @@ def test_ragged_last_window_and_empty_rows():
     assert float(dst.abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("F", [32, 64, 128, 256, 40])
-def test_bulk_copy_kernel_variant(F, monkeypatch):
-    """The warp-specialised bulk-copy (TMA) kernel, selected with TRS_SPMM_KERNEL=bulk, computes the
-    same product; its bounded mbarrier waits report no timeout."""
-    monkeypatch.setenv("TRS_SPMM_KERNEL", "bulk")
-    monkeypatch.setenv("TRS_CHUNK_STEPS", "16")
-    arrays, n = _golden("clustered_n512")
+def _csr_route_format(rp, col, val, keep_sptc_rows=0, part_c=32, short_size=3):
+    """Format arrays that carry rows >= keep_sptc_rows entirely on the CUDA-core route, cut the way
+    split_cuda_row_online does (block_online.cpp:397-439): parts of part_c entries, a tail of at
+    most short_size entries (or a whole row that short) on the short list.  Rows below
+    keep_sptc_rows keep the builder's own routing."""
+    n = rp.numel() - 1
+    head_rp = rp.clone()
+    head_rp[keep_sptc_rows + 1:] = rp[keep_sptc_rows]
+    e_head = int(rp[keep_sptc_rows])
+    arrays, _ = O.build_format(head_rp, col[:e_head], val[:e_head])
+    named = dict(zip(O.FORMAT_NAMES, arrays))
+    lists = {"c": ([0], [], [], []), "cs": ([0], [], [], [])}
+    for k in ("c", "cs"):   # parts the builder already made for the head rows
+        off, row = named[f"{k}_row_offset"].tolist(), named[f"{k}_row"].tolist()
+        lists[k] = (off if off else [0], row, named[f"{k}_column"].tolist(), named[f"{k}_value"].tolist())
+    for r in range(keep_sptc_rows, n):
+        e0, e1 = int(rp[r]), int(rp[r + 1])
+        while e0 < e1:
+            take = min(part_c, e1 - e0)
+            k = "cs" if take <= short_size else "c"
+            off, row, cc, vv = lists[k]
+            row.append(r); cc += col[e0:e0 + take].tolist(); vv += val[e0:e0 + take].tolist()
+            off.append(off[-1] + take)
+            e0 += take
+    for k in ("c", "cs"):
+        off, row, cc, vv = lists[k]
+        named[f"{k}_row_offset"] = torch.tensor(off if row else [], dtype=torch.int32)
+        named[f"{k}_row"] = torch.tensor(row, dtype=torch.int32)
+        named[f"{k}_atomic"] = torch.zeros(len(row), dtype=torch.int32)
+        named[f"{k}_column"] = torch.tensor(cc, dtype=torch.int32)
+        named[f"{k}_value"] = torch.tensor(vv, dtype=torch.float32)
+    return [named[k] for k in O.FORMAT_NAMES]
+
+
+@pytest.mark.parametrize("F", [32, 64, 128, 256, 40, 100])
+@pytest.mark.parametrize("chunk,keep", [("256", 0), ("8", 512)])
+def test_csr_remainder_dominant(F, chunk, keep, monkeypatch):
+    """The CUDA-core remainder (the reference's long and short part kernels, mGCNkernel.cu:976-1042,
+    1119-1171) carrying most or all of the matrix: hub rows with hundreds of parts, single-entry short
+    parts, and - with 8-step items and the first 512 rows left on the tensor-core routes - the parts
+    of split windows spread over the windows' items."""
+    monkeypatch.setenv("TRS_CHUNK_STEPS", chunk)
+    rp, col, val = graphs.rmat_graph(10, 16, seed=12)
+    n = rp.numel() - 1
+    arrays = _csr_route_format(rp, col, val, keep_sptc_rows=keep)
     B = torch.randn(n, F, generator=torch.Generator().manual_seed(F)).half()
     ref = O.spmm_from_format(arrays, B, n)
+    if keep == 0:   # nothing is dropped on this route: the product is A.B itself
+        assert O.scaled_max_error(ref, O.spmm_csr(rp, col, val, B)) <= MAX_ERR_F32
     plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
-    _check(plan.run(B.cuda(), out_dtype=torch.float32), plan.run(B.cuda(), out_dtype=torch.float16), ref)
-    assert plan.status() == 0
+    a = plan.run(B.cuda(), out_dtype=torch.float32)
+    assert torch.equal(a, plan.run(B.cuda(), out_dtype=torch.float32))
+    _check(a, plan.run(B.cuda(), out_dtype=torch.float16), ref)
+    r = plan.run(B.cuda(), out_dtype=torch.float32, relu=True)
+    assert O.scaled_max_error(r.cpu(), torch.relu(ref)) <= MAX_ERR_F32
 
 
-@pytest.mark.parametrize("kernel", ["items", "flat"])
 @pytest.mark.parametrize("name", ["clustered_n512", "rmat_s9_minnnz", "uniform_n250_ragged"])
-def test_both_schedules_agree_with_the_oracle(kernel, name, monkeypatch):
-    """The window-per-CTA schedule (default) and the persistent flat-stream schedule
-    (TRS_SPMM_KERNEL=flat) are separate kernels over the same arrays; both must reproduce the oracle, for several
-    chunk counts of the flat schedule (windows cut at different places)."""
+def test_runs_are_bit_identical_and_relu_epilogue(name):
     arrays, n = _golden(name)
     B = torch.randn(n, 64, generator=torch.Generator().manual_seed(11)).half()
     ref = O.spmm_from_format(arrays, B, n)
-    for per_sm in (["1", "3"] if kernel == "flat" else ["1"]):
-        monkeypatch.setenv("TRS_SPMM_KERNEL", kernel)
-        monkeypatch.setenv("TRS_FLAT_CTAS_PER_SM", per_sm)
-        plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
-        a = plan.run(B.cuda(), out_dtype=torch.float32)
-        b = plan.run(B.cuda(), out_dtype=torch.float32)
-        assert torch.equal(a, b)
-        _check(a, plan.run(B.cuda(), out_dtype=torch.float16), ref)
-        r = plan.run(B.cuda(), out_dtype=torch.float32, relu=True)
-        assert O.scaled_max_error(r.cpu(), torch.relu(ref)) <= MAX_ERR_F32
+    plan = SpmmPlan(Format(arrays).to("cuda"), n, n)
+    a = plan.run(B.cuda(), out_dtype=torch.float32)
+    b = plan.run(B.cuda(), out_dtype=torch.float32)
+    assert torch.equal(a, b)
+    _check(a, plan.run(B.cuda(), out_dtype=torch.float16), ref)
+    r = plan.run(B.cuda(), out_dtype=torch.float32, relu=True)
+    assert O.scaled_max_error(r.cpu(), torch.relu(ref)) <= MAX_ERR_F32
+    assert plan.status() == 0
 
 
 def test_rectangular_matrix_and_wide_features():

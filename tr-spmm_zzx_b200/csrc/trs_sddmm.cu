@@ -37,7 +37,11 @@ constexpr int kUnroll = 8;  // entries in flight per 8-lane group
 template <bool VEC>
 __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, const int* __restrict__ col,
                                                const __half* __restrict__ X, const __half* __restrict__ Y,
-                                               __half* __restrict__ out, int n_rows, long long nnz, int K) {
+                                               __half* __restrict__ out, int n_rows, int n_cols, long long nnz, int K) {
+    // Inputs are not validated by a pass of their own on this entry (trs_sddmm_plan_create does
+    // that for planned patterns), so the kernel bounds what it dereferences: the row walk stops at
+    // the last row, and an entry whose column lies outside [0, n_cols) reads row 0 of Y and is
+    // written as NaN instead of gathering out of range.
     const int lane = threadIdx.x & 31;
     const int sub = lane >> 3, sl = lane & 7;
     const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -60,15 +64,18 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
         for (long long eb = e0; eb < e1; eb += 4 * kUnroll) {
             uint4 yv[kUnroll];
             int rows[kUnroll];
+            unsigned bad = 0;
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 const long long e = eb + sub + 4 * u;
                 rows[u] = -1;
                 yv[u] = make_uint4(0, 0, 0, 0);
                 if (e < e1) {
-                    while ((long long)rowptr[row + 1] <= e) ++row;
+                    while (row + 1 < n_rows && (long long)rowptr[row + 1] <= e) ++row;
                     rows[u] = row;
-                    yv[u] = __ldg(reinterpret_cast<const uint4*>(Y + (size_t)col[e] * 64) + sl);
+                    int c = col[e];
+                    if ((unsigned)c >= (unsigned)n_cols) { c = 0; bad |= 1u << u; }
+                    yv[u] = __ldg(reinterpret_cast<const uint4*>(Y + (size_t)c * 64) + sl);
                 }
             }
 #pragma unroll
@@ -81,7 +88,7 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if (rows[u] >= 0 && sl == 0) out[eb + sub + 4 * u] = __float2half_rn(s);
+                if (rows[u] >= 0 && sl == 0) out[eb + sub + 4 * u] = (bad >> u) & 1u ? __ushort_as_half((unsigned short)0x7e00) : __float2half_rn(s);
             }
         }
         return;
@@ -90,9 +97,11 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
         const long long e = eb + sub;
         const bool live = e < e1;
         float s = 0.f;
+        bool bad = false;
         if (live) {
-            while ((long long)rowptr[row + 1] <= e) ++row;
-            const int c = col[e];
+            while (row + 1 < n_rows && (long long)rowptr[row + 1] <= e) ++row;
+            int c = col[e];
+            if ((unsigned)c >= (unsigned)n_cols) { c = 0; bad = true; }
             const __half* xr = X + (size_t)row * K;
             const __half* yr = Y + (size_t)c * K;
             if (VEC) {
@@ -108,7 +117,7 @@ __global__ void __launch_bounds__(256) k_sddmm(const int* __restrict__ rowptr, c
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (live && sl == 0) out[e] = __float2half_rn(s);
+        if (live && sl == 0) out[e] = bad ? __ushort_as_half((unsigned short)0x7e00) : __float2half_rn(s);
     }
 }
 
@@ -465,9 +474,9 @@ extern "C" int trs_sddmm(const int32_t* rowptr, const int32_t* col, const trs_ha
     const unsigned blocks = (unsigned)trs::ceil_div64(warps, 8);
     const bool vec = (K % 8 == 0) && (((uintptr_t)X & 15) == 0) && (((uintptr_t)Y & 15) == 0);
     if (vec)
-        trs::k_sddmm<true><<<blocks, 256, 0, st>>>(rowptr, col, (const __half*)X, (const __half*)Y, (__half*)out, n_rows, nnz, K);
+        trs::k_sddmm<true><<<blocks, 256, 0, st>>>(rowptr, col, (const __half*)X, (const __half*)Y, (__half*)out, n_rows, n_cols, nnz, K);
     else
-        trs::k_sddmm<false><<<blocks, 256, 0, st>>>(rowptr, col, (const __half*)X, (const __half*)Y, (__half*)out, n_rows, nnz, K);
+        trs::k_sddmm<false><<<blocks, 256, 0, st>>>(rowptr, col, (const __half*)X, (const __half*)Y, (__half*)out, n_rows, n_cols, nnz, K);
     TRS_LAUNCH_CHECK();
     return TRS_OK;
 }

@@ -1,19 +1,24 @@
 // Fused per-window SpMM over the reference's hybrid format, for sm_100a.
 //
-// One CTA owns one work item = a 16-row window (or a slice of a heavy window's k-steps) and all
-// F output features of it.  A "k-step" is 16 columns of the window:
+// One work item = a 16-row window (or a slice of a heavy window's k-steps) and up to 128 output
+// features of it.  A "k-step" is 16 columns of the window:
 //   * a packed 2:4 tile  (s_tile_column / s_packed_a / s_packed_meta, block_online.cpp:796-841)
 //     -> one mma.sp m16n8k16 per 8 features, or
 //   * a pair of dense 16x8 TC blocks (t_column / t_binary / t_value, block_online.cpp:444-540)
 //     -> one dense mma m16n8k16 per 8 features.
-// The 16 B rows of a step are gathered with 16-byte cp.async into a padded shared-memory tile
-// through a multi-stage pipeline and fed to the tensor cores with ldmatrix.trans; accumulation
-// is fp32 in registers across the whole item.  The CSR remainder parts of the window
-// (c_* / cs_* arrays, block_online.cpp:397-439) are added by the lanes that own the row, and C
-// is written exactly once: no memset, no atomics, no second output buffer, no add kernel
-// (compare mGCNkernel_online.cu:1589-1590, 1689-1712).  Heavy windows are cut into several
-// items that write fp32 partial sums to scratch; a second kernel adds them in a fixed order,
-// so results are bit-identical from run to run.
+// The default kernel gives every item to ONE warp: the warp gathers the 16 B rows of a step with
+// 16-byte cp.async into its own padded shared-memory ring, feeds them to the tensor cores with
+// ldmatrix.trans and keeps the fp32 accumulators of all 16 x FS outputs in registers across the
+// item.  No block-wide barrier exists anywhere in the loop; measured on B200, the barrier per
+// k-step of a CTA-cooperative gather, not the bytes in flight, was what held the gather rate at
+// 8.7 TB/s where warp-private rings reach 14 TB/s on the same column stream.
+// The CSR remainder parts of the window (c_* / cs_* arrays, block_online.cpp:397-439; kernels
+// mGCNkernel.cu:976-1042, 1119-1171) are added by the same warp with 16-byte B-row loads, one
+// entry per lane group and a shuffle reduction across the groups, and C is written exactly once:
+// no memset, no atomics, no second output buffer, no add kernel (compare
+// mGCNkernel_online.cu:1589-1590, 1689-1712).  Heavy windows are cut into several items that
+// write fp32 partial sums to scratch; a second kernel adds them in a fixed order, so results are
+// bit-identical from run to run.
 #include <cub/device/device_scan.cuh>
 
 #include <string.h>
@@ -25,13 +30,13 @@
 
 namespace trs {
 
-constexpr int kStages = 4;
+constexpr int kStages = 4;           // CTA-cooperative kernels (fallback for unaligned inputs)
 constexpr int kIdxAhead = 2 * kStages - 2;  // column ids are fetched this many steps ahead
 constexpr int kIdxRing = 8;                 // slots of 16 column ids; >= kIdxAhead + 1
 constexpr int kARegionBytes = 768;   // sparse: 256 B A + 32 B meta; dense: 16 rows x 48 B
 constexpr int kDenseRowHalfs = 24;   // 48-byte row stride of the expanded dense A tile
 
-struct Item {        // 32 bytes: everything a CTA needs to start, in one load
+struct Item {        // 48 bytes: everything a warp / CTA needs to start
     int window;      // window id
     int step_begin;  // k-steps of the window this item covers
     int step_end;
@@ -40,6 +45,10 @@ struct Item {        // 32 bytes: everything a CTA needs to start, in one load
     int ntiles;      // packed tiles of the window (steps [0, ntiles) are tiles, the rest TC pairs)
     int blk0;        // TC block range of the window
     int blk_end;
+    int c_begin;     // long CSR parts this item adds (a split window's parts are spread over its items)
+    int c_end;
+    int cs_begin;    // short CSR parts this item adds
+    int cs_end;
 };
 
 struct Heavy {
@@ -59,14 +68,12 @@ struct WindowRanges {
 
 struct KernelArgs {
     trs_format f;
-    WindowRanges wr;
     const Item* items;
+    int n_items;
     const __half* B;
     void* C;
     float* scratch;
     const __half* tc_dense;        // [blocks][16][8] expanded TC blocks (plan-owned)
-    const unsigned char* zeros;    // 512 zero bytes: source of padded (-1) columns / absent blocks
-    int* status;                   // device word: non-zero after a pipeline wait gave up
     int m_rows, k_cols, window, F, out_half;
     int relu;                      // 1: C = max(A'B, 0) (GCN layer epilogue)
     void* peers[8];                // fused exchange: the fp16 rows are written into every one of these
@@ -115,15 +122,19 @@ __global__ void k_fill_items(trs_format f, WindowRanges wr, int num_windows, int
     int n = item_off[w + 1] - item_off[w];
     const int tile0 = (w < f.num_windows) ? f.s_window_tile_offset[w] : 0;
     const int blk0 = wr.blk_begin[w], blk_end = wr.blk_end[w];
+    const int cb = wr.c_begin[w], cn = wr.c_end[w] - cb, sb = wr.cs_begin[w], sn = wr.cs_end[w] - sb;
     if (n == 1) {
-        items[item_off[w]] = Item{w, 0, steps, -1, tile0, tiles, blk0, blk_end};
+        items[item_off[w]] = Item{w, 0, steps, -1, tile0, tiles, blk0, blk_end, cb, cb + cn, sb, sb + sn};
         return;
     }
-    // split evenly so that no item is much shorter than the others
+    // split evenly so that no item is much shorter than the others; the window's CSR parts are
+    // spread over the items the same way
     int per = (steps + n - 1) / n;
     for (int i = 0; i < n; ++i) {
         int b = min(i * per, steps), e = min(b + per, steps);
-        items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i, tile0, tiles, blk0, blk_end};
+        items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i, tile0, tiles, blk0, blk_end,
+                                      cb + (int)((long long)cn * i / n), cb + (int)((long long)cn * (i + 1) / n),
+                                      sb + (int)((long long)sn * i / n), sb + (int)((long long)sn * (i + 1) / n)};
     }
     heavy[heavy_off[w]] = Heavy{w, slot_off[w], slot_off[w] + n};
 }
@@ -144,27 +155,36 @@ __global__ void k_check_range(const int* __restrict__ a, long long n, int lo, in
     int v = a[i];
     if (v < lo || v >= hi) atomicOr(err, bit);
 }
+// The TC kernels read t_value[t_block_offset[b] + rank] with rank taken from the block's two
+// bitmaps, so the bitmaps' population must equal the block's share of t_value.
+__global__ void k_check_tc_popcount(const long long* __restrict__ t_binary, const int* __restrict__ t_block_offset,
+                                    int blocks, int* err) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    const int bits = __popcll((unsigned long long)t_binary[2 * (size_t)b]) + __popcll((unsigned long long)t_binary[2 * (size_t)b + 1]);
+    if (bits != t_block_offset[b + 1] - t_block_offset[b]) atomicOr(err, V_SHAPE);
+}
 __global__ void k_check_sorted(const int* __restrict__ a, int n, int* err) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i + 1 < n && a[i + 1] < a[i]) atomicOr(err, V_OFFSETS);
 }
 
 // ----------------------------------------------------------------------------------------------
-// the fused window kernel
+// CTA-cooperative kernels
 // ----------------------------------------------------------------------------------------------
-// CSR remainder parts of the window (first item only) and the single write of the item's result:
+// CSR remainder parts of the item and the single write of the item's result:
 // C rows (fp32 or fp16) or, for a slice of a split window, fp32 partial sums in scratch.
 // Accumulators are in mma fragment layout: acc[n][2h + i] = row g + 8h, feature fcol + 8n + i.
 __device__ __forceinline__ void add_csr_parts(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
                                               int wid, int g, int t) {
     const int w = it.window;
     const size_t F = (size_t)a.F;
-    // ---- CSR remainder parts: added by the first item of the window --------------------------
-    if (it.step_begin == 0) {
+    // ---- CSR remainder parts of this item (scalar loop: this path serves unaligned inputs only) ---
+    {
         const int fcol = fbase + wid * 32 + 2 * t;  // + 8*n
         for (int pass = 0; pass < 2; ++pass) {
-            const int pb = pass ? a.wr.cs_begin[w] : a.wr.c_begin[w];
-            const int pe = pass ? a.wr.cs_end[w] : a.wr.c_end[w];
+            const int pb = pass ? it.cs_begin : it.c_begin;
+            const int pe = pass ? it.cs_end : it.c_end;
             const int* roff = pass ? a.f.cs_row_offset : a.f.c_row_offset;
             const int* rrow = pass ? a.f.cs_row : a.f.c_row;
             const int* rcol = pass ? a.f.cs_column : a.f.c_column;
@@ -609,164 +629,308 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArg
 }
 
 // ----------------------------------------------------------------------------------------------
-// Warp-specialised variant: one producer warp feeds the stages with bulk (TMA) copies, WARPS
-// consumer warps only wait, load fragments and issue MMAs.  Per k-step the producer issues one
-// 256-byte-class bulk copy per B row (lanes 0..15) plus the A operand (lanes 16, 17), all
-// completing on the stage's "full" mbarrier; consumers release the stage through its "empty"
-// mbarrier.  This removes the per-thread address arithmetic and the block-wide barrier of the
-// cp.async variant from the inner loop, which ncu showed to be instruction-issue bound.
-// Requirements (checked by the launcher): F % 8 == 0 and 16-byte aligned B and format arrays.
-// Every mbarrier wait is bounded; on a timeout the CTA records it in *status and stops.
+// Default kernel: one warp per work item, no block-wide synchronisation.
 // ----------------------------------------------------------------------------------------------
-constexpr int kBulkStages = 6;
-
-template <int WARPS>
-struct BulkTile {
-    static constexpr int FS = WARPS * 32;
+// FS = features per warp (32 / 64 / 128; F > FS adds feature slabs on gridDim.y).  Per k-step the
+// warp copies the 16 gathered rows (FS * 2 bytes each) with 16 / (256 / FS) cp.async instructions
+// of 16 bytes per lane into a stage of its own ring (row pitch FS * 2 + 16 bytes: conflict-free
+// ldmatrix), the A operand (256 B packed values + 32 B metadata, or two expanded TC blocks) into
+// the same stage, and the column ids of a later step into a small id ring.  Commit groups give the
+// ordering (see the group accounting at the loop); lanes meet in one __syncwarp per step.
+// Requirements (checked by the launcher): F % 8 == 0, B / C / scratch and the tile arrays 16-byte
+// aligned.
+template <int FS, int STAGES>
+struct WarpTile {
+    static constexpr int NT = FS / 8;               // n-tiles (8 features) per warp
+    static constexpr int CPR = FS / 8;              // 16-byte chunks per gathered row
+    static constexpr int RPI = 32 / CPR;            // rows one cp.async warp-instruction covers
+    static constexpr int NCP = 16 / RPI;            // cp.async instructions per lane and step
     static constexpr int ROWB = FS * 2 + 16;
     static constexpr int BBYTES = 16 * ROWB;
-    static constexpr int ABYTES = 512;  // sparse: 256 B A + 32 B meta; dense: two 16x8 blocks
-    static constexpr int STAGE = BBYTES + ABYTES;
-    static constexpr int IDS_OFF = STAGE * kBulkStages;
-    static constexpr int BAR_OFF = IDS_OFF + 1024;
-    static constexpr int SMEM = BAR_OFF + 16 * kBulkStages;
-    static constexpr int THREADS = (WARPS + 1) * 32;
+    static constexpr int STAGE = BBYTES + 512;      // + A operand
+    static constexpr int RING = 8;                  // id ring slots (64 B each), > 2 * STAGES - 2
+    static constexpr int IDA = 2 * STAGES - 2;      // ids run this many steps ahead
+    static constexpr int SMEM = STAGE * STAGES + RING * 64;
+    static_assert(STAGES >= 2 && STAGES <= 4, "id ring holds 8 steps");
+    static_assert(SMEM >= 16 * (FS * 4 + 16), "the epilogue stages a 16 x FS fp32 tile in the ring");
 };
 
-template <int WARPS>
-__global__ void __launch_bounds__((WARPS + 1) * 32) k_window_spmm_bulk(const KernelArgs a) {
-    using T = BulkTile<WARPS>;
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int wid = tid >> 5;
-    const int fbase = blockIdx.y * T::FS;
-
-    const Item it = a.items[blockIdx.x];
-    const int tile0 = it.tile0, ntiles = it.ntiles, blk0 = it.blk0, blk_end = it.blk_end;
-    const int nsteps = it.step_end - it.step_begin;
-    const size_t F = (size_t)a.F;
-    const uint32_t full0 = smem_u32(smem + T::BAR_OFF);
-    const uint32_t empty0 = full0 + 8 * kBulkStages;
-
-    if (tid == 0) {
-        for (int s = 0; s < kBulkStages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, WARPS);
-        }
-        mbar_init_fence();
-    }
-    __syncthreads();
-
-    if (wid == WARPS) {
-        // ------------------------------ producer warp -----------------------------------------
-        const uint32_t rowbytes = (uint32_t)min(T::FS, a.F - fbase) * 2u;
-        int* ids = (int*)(smem + T::IDS_OFF);
-        int4 nx0, nx1;  // this lane's share of the next 16 steps' column ids
-        auto load_ids = [&](int base) {  // lane l: step base + l/2, columns (l%2)*8 .. +7
-            nx0 = make_int4(-1, -1, -1, -1);
-            nx1 = nx0;
-            const int m = base + (lane >> 1);
-            if (m >= nsteps) return;
-            const int s = it.step_begin + m;
-            const int4* src = nullptr;
-            if (s < ntiles) src = (const int4*)(a.f.s_tile_column + (size_t)(tile0 + s) * 16 + (lane & 1) * 8);
-            else {
-                const int b = blk0 + 2 * (s - ntiles) + (lane & 1);
-                if (b < blk_end) src = (const int4*)(a.f.t_column + (size_t)b * 8);
-            }
-            if (src) { nx0 = __ldg(src); nx1 = __ldg(src + 1); }
-        };
-        load_ids(0);
-        bool ok = true;
-        for (int j = 0; j < nsteps; ++j) {
-            if ((j & 15) == 0) {
-                __syncwarp();
-                ((int4*)ids)[lane * 2] = nx0;
-                ((int4*)ids)[lane * 2 + 1] = nx1;
-                __syncwarp();
-                load_ids(j + 16);
-            }
-            const int st = j % kBulkStages;
-            const uint32_t ph = (uint32_t)(j / kBulkStages) & 1u;
-            if (!mbar_wait_bounded(empty0 + 8 * st, ph ^ 1u)) { ok = false; break; }
-            const int s = it.step_begin + j;
-            unsigned char* stp = smem + st * T::STAGE;
-            const uint32_t bar = full0 + 8 * st;
-            const bool sparse = s < ntiles;
-            if (lane == 0) mbar_arrive_expect_tx(bar, 16u * rowbytes + (sparse ? 288u : 512u));
-            __syncwarp();
-            if (lane < 16) {
-                const int c = ids[(j & 15) * 16 + lane];
-                const void* src = c >= 0 ? (const void*)(a.B + (size_t)c * F + fbase) : (const void*)a.zeros;
-                bulk_g2s(smem_u32(stp + lane * T::ROWB), src, rowbytes, bar);
-            } else if (lane == 16) {
-                const void* src = sparse ? (const void*)(a.f.s_packed_a + (size_t)(tile0 + s) * 64)
-                                         : (const void*)(a.tc_dense + (size_t)(blk0 + 2 * (s - ntiles)) * 128);
-                bulk_g2s(smem_u32(stp + T::BBYTES), src, 256u, bar);
-            } else if (lane == 17) {
-                if (sparse) {
-                    bulk_g2s(smem_u32(stp + T::BBYTES + 256), a.f.s_packed_meta + (size_t)(tile0 + s) * 8, 32u, bar);
-                } else {
-                    const int b = blk0 + 2 * (s - ntiles) + 1;
-                    const void* src = b < blk_end ? (const void*)(a.tc_dense + (size_t)b * 128) : (const void*)a.zeros;
-                    bulk_g2s(smem_u32(stp + T::BBYTES + 256), src, 256u, bar);
+// Adds the item's CSR remainder parts into a zeroed 16 x FS fp32 tile in shared memory.  A group
+// of FS / 8 lanes reads one B row segment with 16-byte loads; the 32 / (FS / 8) groups of the warp
+// take different entries of the part and their partial sums meet in a shuffle reduction.
+template <int FS>
+__device__ __forceinline__ void csr_parts_to_tile(const Item& it, const KernelArgs& a, int fbase, int lane, float* tile) {
+    constexpr int LPR = FS / 8, G = 32 / LPR, PITCH = FS + 4;  // floats
+    const int grp = lane / LPR, ch = lane % LPR;
+    const int f = fbase + ch * 8;
+    const bool fin = f < a.F;
+    const uint4* Bq = (const uint4*)a.B;
+    const uint32_t pitch16 = (uint32_t)a.F >> 3;
+    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;
+    for (int pass = 0; pass < 2; ++pass) {
+        const int pb = pass ? it.cs_begin : it.c_begin;
+        const int pe = pass ? it.cs_end : it.c_end;
+        const int* roff = pass ? a.f.cs_row_offset : a.f.c_row_offset;
+        const int* rrow = pass ? a.f.cs_row : a.f.c_row;
+        const int* rcol = pass ? a.f.cs_column : a.f.c_column;
+        const __half* rval = (const __half*)(pass ? a.f.cs_value : a.f.c_value);
+        for (int p = pb; p < pe; ++p) {
+            const int lr = __ldg(rrow + p) - it.window * a.window;
+            const int e0 = __ldg(roff + p), e1 = __ldg(roff + p + 1);
+            float s[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i] = 0.f;
+            for (int e = e0 + grp; e < e1; e += G) {
+                const int c = __ldg(rcol + e);
+                const float v = __half2float(__ldg(rval + e));
+                if (fin) {
+                    const uint4 q = __ldg(Bq + (size_t)((uint32_t)c * pitch16 + chunk16));
+                    const __half2* h = (const __half2*)&q;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 x = __half22float2(h[i]);
+                        s[2 * i] = fmaf(v, x.x, s[2 * i]);
+                        s[2 * i + 1] = fmaf(v, x.y, s[2 * i + 1]);
+                    }
                 }
             }
-        }
-        if (!ok && lane == 0) atomicExch(a.status, 1);
-        return;
-    }
-
-    // ---------------------------------- consumer warps ------------------------------------------
-    const int g = lane >> 2, t = lane & 3;
-    float acc[4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+            for (int off = LPR; off < 32; off <<= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], off);
+            if (grp == 0 && lr >= 0 && lr < 16) {
+                float4* d = (float4*)(tile + lr * PITCH + ch * 8);
+                float4 u = d[0], w = d[1];
+                u.x += s[0]; u.y += s[1]; u.z += s[2]; u.w += s[3];
+                w.x += s[4]; w.y += s[5]; w.z += s[6]; w.w += s[7];
+                d[0] = u; d[1] = w;
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// Epilogue of a warp-owned item.  Accumulators are in mma fragment layout: acc[n][2h + i] = row
+// g + 8h, feature fbase + 8n + 2t + i.  The result tile is staged in the warp's (drained) ring and
+// leaves in 16-byte pieces of whole rows: fp32 partial sums to a scratch slot, or fp16 / fp32
+// rows of C, or fp16 rows into every peer buffer of the fused exchange.
+template <int FS>
+__device__ __forceinline__ void finish_item_warp(float (&acc)[FS / 8][4], const Item& it, const KernelArgs& a, int fbase,
+                                                 int lane, unsigned char* ring) {
+    constexpr int NT = FS / 8;
+    const int g = lane >> 2, t = lane & 3;
+    if (it.c_end > it.c_begin || it.cs_end > it.cs_begin) {
+        constexpr int PITCH = FS + 4;
+        float* tile = (float*)ring;
+        for (int i = lane; i < 16 * PITCH / 4; i += 32) ((float4*)tile)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncwarp();
+        csr_parts_to_tile<FS>(it, a, fbase, lane, tile);
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float2 x = *(const float2*)(tile + (g + 8 * h) * PITCH + 8 * n + 2 * t);
+                acc[n][2 * h] += x.x;
+                acc[n][2 * h + 1] += x.y;
+            }
+        __syncwarp();
+    }
+    const bool partial = it.slot >= 0;
+    if (a.relu && !partial) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][i] = fmaxf(acc[n][i], 0.f);
+    }
+    const bool half_out = !partial && (a.out_half || a.n_peers > 0);
+    if (half_out) {
+        constexpr int PITCH = FS * 2 + 16;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                *(__half2*)(ring + (g + 8 * h) * PITCH + (8 * n + 2 * t) * 2) = __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]);
+        __syncwarp();
+        constexpr int CPR = FS / 8;
+        for (int c = lane; c < 16 * CPR; c += 32) {
+            const int lr = c / CPR, ch = c % CPR;
+            const int f = fbase + ch * 8;
+            const long long row = (long long)it.window * a.window + lr;
+            if (lr >= a.window || row >= a.m_rows || f >= a.F) continue;
+            const uint4 v = *(const uint4*)(ring + lr * PITCH + ch * 16);
+            if (a.n_peers > 0) {
+                const size_t off = (size_t)(a.peer_row0 + row) * (size_t)a.F + f;
+                for (int d = 0; d < a.n_peers; ++d) *(uint4*)((__half*)a.peers[d] + off) = v;
+            } else {
+                __stcs((uint4*)((__half*)a.C + (size_t)row * a.F + f), v);
+            }
+        }
+    } else {
+        constexpr int PITCH = FS * 4 + 16;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                *(float2*)(ring + (g + 8 * h) * PITCH + (8 * n + 2 * t) * 4) = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+        __syncwarp();
+        constexpr int CPR = FS / 4;
+        float* dst = partial ? a.scratch + (size_t)it.slot * 16 * (size_t)a.F : (float*)a.C;
+        for (int c = lane; c < 16 * CPR; c += 32) {
+            const int lr = c / CPR, ch = c % CPR;
+            const int f = fbase + ch * 4;
+            const long long row = (long long)it.window * a.window + lr;
+            if (f >= a.F) continue;
+            if (!partial && (lr >= a.window || row >= a.m_rows)) continue;
+            const float4 v = *(const float4*)(ring + lr * PITCH + ch * 16);
+            float4* d = (float4*)(dst + (partial ? (size_t)lr : (size_t)row) * a.F + f);
+            if (partial) *d = v;
+            else __stcs(d, v);
+        }
+    }
+}
+
+template <int FS, int STAGES, int MINB>
+__global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs a) {
+    using T = WarpTile<FS, STAGES>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x;
+    const int g = lane >> 2;
+    const int fbase = blockIdx.y * FS;
+
+    const Item it = a.items[blockIdx.x];
+    const int nsteps = it.step_end - it.step_begin;
+    const int nsparse = min(max(it.ntiles - it.step_begin, 0), nsteps);  // steps [0, nsparse) are packed tiles
+
+    const uint32_t smem0 = smem_u32(smem);
+    const uint32_t ring0 = smem0 + T::STAGE * STAGES;
+    const unsigned char* ringp = smem + T::STAGE * STAGES;
+
+    // gather role of this lane: chunk `ch` of rows sub * NCP + k, k = 0 .. NCP-1
+    const int ch = lane % T::CPR, sub = lane / T::CPR;
+    const uint32_t pitch16 = (uint32_t)a.F >> 3;             // 16-byte units per B row
+    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;    // this lane's chunk inside a row
+    const bool fin = fbase + ch * 8 < a.F;
+    const uint4* Bq = (const uint4*)a.B;
+    const uint32_t dst0 = smem0 + (sub * T::NCP) * T::ROWB + ch * 16;
+    // ldmatrix role: matrix lane / 8 -> k rows (m & 1) * 8 .., features (m >> 1) * 8 ..
+    const int mtx = lane >> 3;
+    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + ((mtx >> 1) * 8) * 2;
+
+    float acc[T::NT][4];
+#pragma unroll
+    for (int i = 0; i < T::NT; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    const int m = lane >> 3;
-    const int krow = (lane & 7) + (m & 1) * 8;
-    const uint32_t boff = krow * T::ROWB + (wid * 32 + (m >> 1) * 8) * 2;
-    bool ok = true;
-    for (int j = 0; j < nsteps; ++j) {
-        const int st = j % kBulkStages;
-        const uint32_t ph = (uint32_t)(j / kBulkStages) & 1u;
-        if (!mbar_wait_bounded(full0 + 8 * st, ph)) { ok = false; break; }
-        const unsigned char* stp = smem + st * T::STAGE;
-        const unsigned char* as = stp + T::BBYTES;
-        const uint32_t baddr = smem_u32(stp) + boff;
-        if (it.step_begin + j < ntiles) {
+
+    auto issue_idx = [&](int m) {
+        if (lane < 4 && m < nsteps) {
+            const int s = it.step_begin + m;
+            const uint32_t dst = ring0 + (m & (T::RING - 1)) * 64 + lane * 16;
+            if (s < it.ntiles) {
+                cp_async16(dst, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + lane * 4, 16);
+            } else {
+                const int b = it.blk0 + 2 * (s - it.ntiles) + (lane >> 1);
+                if (b < it.blk_end) cp_async16(dst, a.f.t_column + (size_t)b * 8 + (lane & 1) * 4, 16);
+                else *(int4*)(smem + T::STAGE * STAGES + (m & (T::RING - 1)) * 64 + lane * 16) = make_int4(-1, -1, -1, -1);
+            }
+        }
+    };
+
+    auto issue = [&](int j, int stage) {
+        const int* cols = (const int*)(ringp + (j & (T::RING - 1)) * 64) + sub * T::NCP;
+        int c[T::NCP];
+        if constexpr (T::NCP == 8) {
+            const int4 x = *(const int4*)cols, y = *(const int4*)(cols + 4);
+            c[0] = x.x; c[1] = x.y; c[2] = x.z; c[3] = x.w;
+            c[4] = y.x; c[5] = y.y; c[6] = y.z; c[7] = y.w;
+        } else if constexpr (T::NCP == 4) {
+            const int4 x = *(const int4*)cols;
+            c[0] = x.x; c[1] = x.y; c[2] = x.z; c[3] = x.w;
+        } else {
+            const int2 x = *(const int2*)cols;
+            c[0] = x.x; c[1] = x.y;
+        }
+        const uint32_t d = dst0 + stage * T::STAGE;
+#pragma unroll
+        for (int k = 0; k < T::NCP; ++k) {
+            const uint32_t o = (uint32_t)max(c[k], 0) * pitch16 + chunk16;
+            cp_async16(d + k * T::ROWB, Bq + o, (c[k] >= 0 && fin) ? 16 : 0);
+        }
+        // A operand
+        const int s = it.step_begin + j;
+        const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + lane * 16;
+        if (s < it.ntiles) {
+            const size_t tile = (size_t)(it.tile0 + s);
+            if (lane < 16) cp_async16(adst, a.f.s_packed_a + tile * 64 + lane * 4, 16);
+            else if (lane < 18) cp_async16(adst, a.f.s_packed_meta + tile * 8 + (lane - 16) * 4, 16);
+        } else {
+            const int b = it.blk0 + 2 * (s - it.ntiles) + (lane >> 4);
+            const bool live = b < it.blk_end;
+            cp_async16(adst, a.tc_dense + (size_t)(live ? b : it.blk0) * 128 + (lane & 15) * 8, live ? 16 : 0);
+        }
+    };
+
+    auto compute = [&](int j, int stage) {
+        const unsigned char* as = smem + stage * T::STAGE + T::BBYTES;
+        const uint32_t baddr = boff + stage * T::STAGE;
+        if (j < nsparse) {
             const uint2 av = *(const uint2*)(as + lane * 8);
             const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < T::NT / 2; ++h) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
                 mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
                 mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
             }
         } else {
+            const int t = lane & 3;
             const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
             const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
             const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
             const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < T::NT / 2; ++h) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
                 mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
                 mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * st);
+    };
+
+    // Group accounting.  The prologue group carries the ids of steps 0 .. IDA-1 and is waited for
+    // in full.  Then group k (k = 0, 1, ...) carries the rows of step k and, from k = STAGES-1 on,
+    // the ids of step k - (STAGES-1) + IDA.  At iteration j all groups but the newest STAGES-2 are
+    // complete, i.e. groups 0 .. j: the rows of step j, and the ids up to step j + IDA - STAGES + 1
+    // = j + STAGES - 1, exactly what the gather issued in this iteration reads.
+#pragma unroll
+    for (int m = 0; m < T::IDA; ++m) issue_idx(m);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < STAGES - 1; ++j) {
+        if (j < nsteps) issue(j, j);
+        cp_async_commit();
     }
-    if (!ok) {
-        if (lane == 0) atomicExch(a.status, 2);
-        return;
+    for (int j0 = 0; j0 < nsteps; j0 += STAGES) {
+#pragma unroll
+        for (int u = 0; u < STAGES; ++u) {
+            const int j = j0 + u;
+            if (j < nsteps) {
+                cp_async_wait<STAGES - 2>();
+                __syncwarp();
+                issue_idx(j + T::IDA);
+                if (j + STAGES - 1 < nsteps) issue(j + STAGES - 1, (u + STAGES - 1) % STAGES);
+                cp_async_commit();
+                compute(j, u);
+            }
+        }
     }
-    finish_item(acc, it, a, fbase, wid, g, t);
+    cp_async_wait<0>();
+    __syncwarp();
+    finish_item_warp<FS>(acc, it, a, fbase, lane, smem);
 }
 
 // Expands the bitmap + packed values of every TC block into a dense 16x8 fp16 tile.
@@ -786,277 +950,6 @@ __global__ void k_expand_tc(const long long* __restrict__ t_binary, const int* _
         v = t_value[(size_t)t_block_offset[b] + rank];
     }
     dense[i] = v;
-}
-
-// ----------------------------------------------------------------------------------------------
-// Persistent "flat stream" variant.  All k-steps of the matrix form one list ordered by window
-// (a window's packed tiles, then its TC block pairs); the plan cuts the list into one contiguous
-// chunk per resident CTA, balanced by steps plus a fixed cost per window.  A CTA streams through
-// its chunk with the gather pipeline never draining: when a window ends it writes the 16 rows
-// while the loads of the next windows are already in flight.  This removes the per-window
-// pipeline fill / drain of the item-per-CTA kernels, which dominates for windows of a few dozen
-// steps.  Per step the kernel reads an 8-byte descriptor (tile or TC-pair index, window id,
-// first/last-of-window flags) that runs kMetaAhead steps ahead of the compute; column ids run
-// kIdxAhead ahead and B rows kStages-1 ahead, all through cp.async groups.
-// Windows cut by a chunk boundary write fp32 partial sums to two fixed scratch slots per CTA;
-// k_reduce_flat adds them in chunk order (deterministic).
-// ----------------------------------------------------------------------------------------------
-constexpr int kMetaAhead = 10;
-constexpr int kMetaRing = 16;
-constexpr unsigned kDescLast = 0x80000000u, kDescFirst = 0x40000000u, kDescTc = 0x20000000u,
-                   kDescTcSecond = 0x10000000u, kDescIndex = 0x0FFFFFFFu;
-
-struct FlatArgs {
-    const int2* meta;         // [S] {descriptor, window}
-    const int* chunk_begin;   // [G + 1]
-    int G;
-};
-
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_flat(const KernelArgs a, const FlatArgs fa) {
-    using T = Tile<WARPS>;
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int wid = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int fbase = blockIdx.y * T::FS;
-    const int chunk = blockIdx.x;
-    const int g0 = fa.chunk_begin[chunk];
-    const int nsteps = fa.chunk_begin[chunk + 1] - g0;
-    if (nsteps <= 0) return;
-
-    const uint32_t smem0 = smem_u32(smem);
-    constexpr int RING_OFF = T::STAGE * kStages;            // ids ring: kIdxRing x 64 B
-    constexpr int META_OFF = RING_OFF + kIdxRing * 64;      // meta ring: kMetaRing x 8 B
-    const int* ring = (const int*)(smem + RING_OFF);
-    const int2* mring = (const int2*)(smem + META_OFF);
-
-    const int ch = tid % T::CPR, row0 = tid / T::CPR;
-    const uint32_t pitch16 = (uint32_t)a.F >> 3;
-    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;
-    const bool fin = fbase + ch * 8 < a.F;
-    const uint4* Bq = (const uint4*)a.B;
-    const uint32_t dst0 = smem0 + row0 * T::ROWB + ch * 16;
-    const int mtx = lane >> 3;
-    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + (wid * 32 + (mtx >> 1) * 8) * 2;
-    const unsigned char* a_lane = smem + T::BBYTES;
-
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-    auto issue_meta = [&](int m) {
-        if (tid == 0 && m < nsteps)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem0 + META_OFF + (m & (kMetaRing - 1)) * 8),
-                         "l"(fa.meta + (size_t)(g0 + m)));
-    };
-    auto issue_idx = [&](int m) {
-        if (tid < 4 && m < nsteps) {
-            const unsigned desc = (unsigned)mring[m & (kMetaRing - 1)].x;
-            const unsigned index = desc & kDescIndex;
-            const uint32_t dst = smem0 + RING_OFF + (m & (kIdxRing - 1)) * 64 + tid * 16;
-            if (!(desc & kDescTc)) {
-                cp_async16(dst, a.f.s_tile_column + (size_t)index * 16 + tid * 4, 16);
-            } else if (tid < 2 || (desc & kDescTcSecond)) {
-                cp_async16(dst, a.f.t_column + (size_t)(index + (tid >> 1)) * 8 + (tid & 1) * 4, 16);
-            } else {
-                *(int4*)(smem + RING_OFF + (m & (kIdxRing - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
-            }
-        }
-    };
-    auto issue = [&](int j, int stage) {
-        const int* cols = ring + (j & (kIdxRing - 1)) * 16;
-        const int c0 = cols[row0], c1 = cols[row0 + 8];
-        const uint32_t o0 = (uint32_t)max(c0, 0) * pitch16 + chunk16;
-        const uint32_t o1 = (uint32_t)max(c1, 0) * pitch16 + chunk16;
-        cp_async16(dst0 + stage * T::STAGE, Bq + o0, (c0 >= 0 && fin) ? 16 : 0);
-        cp_async16(dst0 + stage * T::STAGE + 8 * T::ROWB, Bq + o1, (c1 >= 0 && fin) ? 16 : 0);
-        if (tid < 32) {
-            const unsigned desc = (unsigned)mring[j & (kMetaRing - 1)].x;
-            const size_t index = desc & kDescIndex;
-            const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + tid * 16;
-            if (!(desc & kDescTc)) {
-                if (tid < 16) cp_async16(adst, a.f.s_packed_a + index * 64 + tid * 4, 16);
-                else if (tid < 18) cp_async16(adst, a.f.s_packed_meta + index * 8 + (tid - 16) * 4, 16);
-            } else {
-                const bool live = tid < 16 || (desc & kDescTcSecond);
-                cp_async16(adst, a.tc_dense + (index + (live ? (tid >> 4) : 0)) * 128 + (tid & 15) * 8, live ? 16 : 0);
-            }
-        }
-    };
-    auto compute = [&](bool dense, int stage) {
-        const unsigned char* as = a_lane + stage * T::STAGE;
-        const uint32_t baddr = boff + stage * T::STAGE;
-        if (!dense) {
-            const uint2 av = *(const uint2*)(as + lane * 8);
-            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
-                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
-            }
-        } else {
-            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
-            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
-            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
-            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
-                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
-            }
-        }
-    };
-
-    // ---- prologue: three dependent fills, paid once per chunk -------------------------------------
-#pragma unroll
-    for (int m = 0; m < kMetaAhead; ++m) issue_meta(m);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-#pragma unroll
-    for (int m = 0; m < kIdxAhead; ++m) issue_idx(m);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < kStages - 1; ++j) {
-        if (j < nsteps) issue(j, j);
-        cp_async_commit();
-    }
-    bool piece_first = true;  // does the current piece contain its window's first step?  (set below)
-    bool piece_open = false;
-    for (int j0 = 0; j0 < nsteps; j0 += kStages) {
-#pragma unroll
-        for (int u = 0; u < kStages; ++u) {
-            const int j = j0 + u;
-            if (j < nsteps) {
-                cp_async_wait<kStages - 2>();
-                __syncthreads();
-                issue_meta(j + kMetaAhead);
-                issue_idx(j + kIdxAhead);
-                if (j + kStages - 1 < nsteps) issue(j + kStages - 1, (u + kStages - 1) % kStages);
-                cp_async_commit();
-                const int2 mt = mring[j & (kMetaRing - 1)];
-                const unsigned desc = (unsigned)mt.x;
-                if (!piece_open) { piece_open = true; piece_first = (desc & kDescFirst) != 0; }
-                compute((desc & kDescTc) != 0, u);
-                if ((desc & kDescLast) || j == nsteps - 1) {
-                    // the piece ends here: whole window -> C; otherwise a partial-sum slot
-                    const bool whole = piece_first && (desc & kDescLast);
-                    Item it;
-                    it.window = mt.y;
-                    it.step_begin = piece_first ? 0 : 1;  // only the piece with the first step adds the CSR parts
-                    it.step_end = 0;
-                    it.slot = whole ? -1 : (piece_first ? 2 * chunk + 1 : 2 * chunk);
-                    it.tile0 = it.ntiles = it.blk0 = it.blk_end = 0;
-                    finish_item(acc, it, a, fbase, wid, g, t);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) acc[i][k] = 0.f;
-                    piece_open = false;
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
-}
-
-// Windows without any k-step (empty, or CSR parts only): zeros plus the CSR parts.
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) k_window_nosteps(const KernelArgs a, const int* __restrict__ windows) {
-    using T = Tile<WARPS>;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    Item it;
-    it.window = windows[blockIdx.x];
-    it.step_begin = 0; it.step_end = 0; it.slot = -1;
-    it.tile0 = it.ntiles = it.blk0 = it.blk_end = 0;
-    finish_item(acc, it, a, blockIdx.y * T::FS, wid, lane >> 2, lane & 3);
-}
-
-// One block per chunk boundary: if the boundary cuts a window and is the first cut of that window,
-// add the window's pieces in chunk order and write its rows.
-__global__ void k_reduce_flat(const FlatArgs fa, const float* __restrict__ scratch, void* C, int F, int m_rows, int window,
-                              int out_half, int relu) {
-    const int c = blockIdx.x + 1;  // boundary between chunk c-1 and chunk c
-    const int b = fa.chunk_begin[c];
-    if (b <= fa.chunk_begin[c - 1] && c > 1) {
-        // empty chunk c-1: the cut (if any) belongs to an earlier boundary with the same position
-        if (fa.chunk_begin[c - 1] == b) return;
-    }
-    if (b >= fa.chunk_begin[fa.G]) return;
-    const int2 here = fa.meta[b];
-    if ((unsigned)here.x & kDescFirst) return;  // the boundary falls between two windows
-    const int w = here.y;
-    // first cut of this window?  the chunk before must hold the window's first step
-    int cp = c - 1;
-    while (cp > 0 && fa.chunk_begin[cp] == b) --cp;  // skip empty chunks at the same position
-    const int pb = fa.chunk_begin[cp];
-    if (fa.meta[pb].y == w && !((unsigned)fa.meta[pb].x & kDescFirst)) return;  // the window was already cut earlier
-    const int per = 16 * F;
-    for (int i = threadIdx.x; i < per; i += blockDim.x) {
-        const int lr = i / F, f = i % F;
-        const long long row = (long long)w * window + lr;
-        if (lr >= window || row >= m_rows) continue;
-        float s = scratch[(size_t)(2 * cp + 1) * per + i];  // tail piece of the chunk with the first step
-        for (int cc = c; cc < fa.G; ++cc) {
-            const int bb = fa.chunk_begin[cc];
-            if (bb >= fa.chunk_begin[cc + 1]) continue;  // empty chunk
-            const int2 m2 = fa.meta[bb];
-            if (m2.y != w || ((unsigned)m2.x & kDescFirst)) break;
-            s += scratch[(size_t)(2 * cc) * per + i];       // head piece of a later chunk
-        }
-        if (relu) s = fmaxf(s, 0.f);
-        if (out_half) ((__half*)C)[(size_t)row * F + f] = __float2half_rn(s);
-        else ((float*)C)[(size_t)row * F + f] = s;
-    }
-}
-
-// step descriptors: one thread per step
-__global__ void k_fill_meta(trs_format f, WindowRanges wr, const int* __restrict__ win_step_off, int W, int S,
-                            int2* __restrict__ meta) {
-    const int s = blockIdx.x * blockDim.x + threadIdx.x;
-    if (s >= S) return;
-    int lo = 0, hi = W;
-    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (win_step_off[mid] <= s) lo = mid; else hi = mid; }
-    const int w = lo;
-    const int first = win_step_off[w], last = win_step_off[w + 1] - 1;
-    const int tile0 = w < f.num_windows ? f.s_window_tile_offset[w] : 0;
-    const int ntiles = w < f.num_windows ? f.s_window_tile_offset[w + 1] - tile0 : 0;
-    const int local = s - first;
-    unsigned desc;
-    if (local < ntiles) desc = (unsigned)(tile0 + local);
-    else {
-        const int blk = wr.blk_begin[w] + 2 * (local - ntiles);
-        desc = kDescTc | (unsigned)blk | (blk + 1 < wr.blk_end[w] ? kDescTcSecond : 0u);
-    }
-    if (s == first) desc |= kDescFirst;
-    if (s == last) desc |= kDescLast;
-    meta[s] = make_int2((int)desc, w);
-}
-
-__global__ void k_window_steps(trs_format f, WindowRanges wr, int W, int* __restrict__ steps) {
-    const int w = blockIdx.x * blockDim.x + threadIdx.x;
-    if (w > W) return;
-    int n = 0;
-    if (w < W) {
-        if (w < f.num_windows) n = f.s_window_tile_offset[w + 1] - f.s_window_tile_offset[w];
-        n += (wr.blk_end[w] - wr.blk_begin[w] + 1) / 2;
-    }
-    steps[w] = n;
 }
 
 // Adds the partial sums of a split window in slot order and writes its 16 rows of C.
@@ -1094,21 +987,12 @@ using namespace trs;
 struct trs_spmm_plan {
     trs_format f;
     int m_rows, k_cols, window, num_windows, chunk;
-    DevBuf<int> ranges;  // 6 * num_windows
-    WindowRanges wr;
     DevBuf<Item> items;
     DevBuf<Heavy> heavy;
-    DevBuf<__half> tc_dense;          // expanded TC blocks for the bulk-copy kernel
-    DevBuf<unsigned char> zeros;      // 512 zero bytes + the status word behind them
+    DevBuf<__half> tc_dense;          // TC blocks expanded to dense 16 x 8 fp16 tiles
     int n_items, n_heavy, n_slots;
     std::vector<int> h_item_off, h_heavy_off;  // host copies of the per-window prefixes (num_windows + 1 each)
-    bool bulk_ok;                     // bulk-copy kernel requested and usable
     bool arrays_aligned;              // index / tile arrays are 16-byte aligned
-    // persistent flat-stream kernel
-    bool flat_ok = false;
-    int flat_G = 0, flat_S = 0, n_nosteps = 0;
-    DevBuf<int2> step_meta;
-    DevBuf<int> chunk_begin, nosteps;
 };
 
 static int env_int(const char* name, int dflt) {
@@ -1138,6 +1022,17 @@ static int validate_on_device(const trs_format& f, int m_rows, int k_cols, int w
         k_check_range<<<grid(n), 256, 0, st>>>(row, n, 0, m_rows, V_ROW, d_err);
         k_check_sorted<<<grid(n), 256, 0, st>>>(row, n, d_err);
     }
+    // The checks below size their reads by prefix entries, so the verdict on the prefixes comes first.
+    {
+        int h_pre = 0;
+        cudaError_t e1 = cudaMemcpyAsync(&h_pre, d_err, sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (e1 == cudaSuccess) e1 = cudaStreamSynchronize(st);
+        if (e1 != cudaSuccess) { cudaFree(d_err); return (int)e1; }
+        if (h_pre & V_OFFSETS) { cudaFree(d_err); return TRS_E_OFFSETS; }
+        if (h_pre & V_SHAPE) { cudaFree(d_err); return TRS_E_SHAPE; }
+    }
+    if (f.blocks > 0)
+        k_check_tc_popcount<<<grid(f.blocks), 256, 0, st>>>((const long long*)f.t_binary, f.t_block_offset, f.blocks, d_err);
     // column ids of the CSR parts: their count is the last prefix entry, which lives on the device
     for (int pass = 0; pass < 2; ++pass) {
         const int n = pass ? f.parts_c_short : f.parts_c;
@@ -1164,79 +1059,6 @@ static int validate_on_device(const trs_format& f, int m_rows, int k_cols, int w
     if (h_err & V_COLUMN) return TRS_E_COLUMN;
     if (h_err & V_ROW) return TRS_E_ROW;
     return TRS_OK;
-}
-
-// Flat-stream structures: steps per window -> prefix -> per-step descriptors; the step list is cut
-// into one chunk per resident CTA, balanced by steps + a fixed cost per window end.
-static int build_flat(trs_spmm_plan* p, cudaStream_t st) {
-    const int W = p->num_windows;
-    DevBuf<int> steps, off;
-    DevBuf<unsigned char> tmp;
-    int rc = steps.alloc((size_t)W + 1);
-    if (!rc) rc = off.alloc((size_t)W + 1);
-    auto done = [&](int code) { steps.release(); off.release(); tmp.release(); return code; };
-    if (rc) return done(rc);
-    k_window_steps<<<(unsigned)((W + 1 + 255) / 256), 256, 0, st>>>(p->f, p->wr, W, steps.p);
-    size_t tb = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, tb, steps.p, off.p, W + 1, st);
-    rc = tmp.alloc(tb + 16);
-    if (rc) return done(rc);
-    cub::DeviceScan::ExclusiveSum(tmp.p, tb, steps.p, off.p, W + 1, st);
-    std::vector<int> h_off((size_t)W + 1);
-    cudaError_t e = cudaMemcpyAsync(h_off.data(), off.p, sizeof(int) * ((size_t)W + 1), cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return done((int)e);
-    const int S = h_off[W];
-    p->flat_S = S;
-    // windows without steps get their own tiny kernel
-    std::vector<int> nos;
-    for (int w = 0; w < W; ++w)
-        if (h_off[w + 1] == h_off[w]) nos.push_back(w);
-    p->n_nosteps = (int)nos.size();
-    rc = p->nosteps.alloc(nos.size());
-    if (rc) return done(rc);
-    if (!nos.empty()) cudaMemcpyAsync(p->nosteps.p, nos.data(), sizeof(int) * nos.size(), cudaMemcpyHostToDevice, st);
-    // chunk boundaries
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // one chunk per CTA that can be resident at once (the F = 128 kernel is the largest one)
-    int occ = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_window_spmm_flat<4>, 128, Tile<4>::SMEM + kMetaRing * 8);
-    const int per_sm = max(1, env_int("TRS_FLAT_CTAS_PER_SM", occ > 0 ? occ : 8));
-    int G = sms * per_sm;
-    if (S < G * 8) G = max(1, S / 8);
-    const double win_cost = (double)env_int("TRS_FLAT_WINDOW_COST", 4);
-    std::vector<int> cb((size_t)G + 1, S);
-    cb[0] = 0;
-    if (S > 0) {
-        // cost position of step s inside window w: s + win_cost * (non-empty windows finished before w)
-        const double total = (double)S + win_cost * (double)(W - (int)nos.size());
-        int w = 0;
-        double done_windows = 0;  // non-empty windows fully before w
-        for (int c = 1; c < G; ++c) {
-            const double target = total * c / G;
-            while (w < W && (double)h_off[w + 1] + win_cost * (done_windows + (h_off[w + 1] > h_off[w] ? 1 : 0)) <= target) {
-                if (h_off[w + 1] > h_off[w]) done_windows += 1;
-                ++w;
-            }
-            int s = w < W ? (int)(target - win_cost * done_windows) : S;
-            if (w < W) s = min(max(s, h_off[w]), h_off[w + 1]);
-            cb[c] = max(cb[c - 1], min(s, S));
-        }
-    }
-    p->flat_G = G;
-    rc = p->chunk_begin.alloc((size_t)G + 1);
-    if (!rc) rc = p->step_meta.alloc((size_t)max(S, 1));
-    if (rc) return done(rc);
-    cudaMemcpyAsync(p->chunk_begin.p, cb.data(), sizeof(int) * ((size_t)G + 1), cudaMemcpyHostToDevice, st);
-    if (S > 0)
-        k_fill_meta<<<(unsigned)((S + 255) / 256), 256, 0, st>>>(p->f, p->wr, off.p, W, S, p->step_meta.p);
-    e = cudaStreamSynchronize(st);
-    if (e == cudaSuccess) e = cudaGetLastError();
-    if (e != cudaSuccess) return done((int)e);
-    p->flat_ok = true;
-    return done(0);
 }
 
 // CSR value-count checks need the last prefix entry; done with the column range check so that a
@@ -1272,32 +1094,32 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     p->f = f;
     p->m_rows = m_rows; p->k_cols = k_cols; p->window = window; p->num_windows = W;
     p->chunk = max(8, env_int("TRS_CHUNK_STEPS", 256));
-    int rc = p->ranges.alloc((size_t)6 * W);
-    if (rc) { delete p; return rc; }
-    cudaMemsetAsync(p->ranges.p, 0, sizeof(int) * 6 * W, st);
-    p->wr = WindowRanges{p->ranges.p, p->ranges.p + W, p->ranges.p + 2 * W, p->ranges.p + 3 * W,
-                         p->ranges.p + 4 * W, p->ranges.p + 5 * W};
+    // per-window ranges of TC blocks and CSR parts (needed only while the items are made)
+    DevBuf<int> ranges, cnt, off;
+    DevBuf<unsigned char> tmp;
+    auto fail = [&](int code) { ranges.release(); cnt.release(); off.release(); tmp.release(); trs_spmm_plan_destroy(p); return code; };
+    int rc = ranges.alloc((size_t)6 * W);
+    if (rc) return fail(rc);
+    cudaMemsetAsync(ranges.p, 0, sizeof(int) * 6 * W, st);
+    WindowRanges wr{ranges.p, ranges.p + W, ranges.p + 2 * W, ranges.p + 3 * W, ranges.p + 4 * W, ranges.p + 5 * W};
     auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
     if (f.parts_t > 0)
         k_part_ranges<<<grid(f.parts_t), 256, 0, st>>>(f.t_window_row, f.t_row_offset, f.parts_t, 16, W,
-                                                        p->wr.blk_begin, p->wr.blk_end, 1);
+                                                        wr.blk_begin, wr.blk_end, 1);
     if (f.parts_c > 0)
-        k_part_ranges<<<grid(f.parts_c), 256, 0, st>>>(f.c_row, nullptr, f.parts_c, window, W, p->wr.c_begin, p->wr.c_end, 0);
+        k_part_ranges<<<grid(f.parts_c), 256, 0, st>>>(f.c_row, nullptr, f.parts_c, window, W, wr.c_begin, wr.c_end, 0);
     if (f.parts_c_short > 0)
         k_part_ranges<<<grid(f.parts_c_short), 256, 0, st>>>(f.cs_row, nullptr, f.parts_c_short, window, W,
-                                                              p->wr.cs_begin, p->wr.cs_end, 0);
+                                                              wr.cs_begin, wr.cs_end, 0);
     // counts -> exclusive scans (three arrays of W + 1)
-    DevBuf<int> cnt, off;
-    DevBuf<unsigned char> tmp;
     rc = cnt.alloc((size_t)3 * (W + 1));
     if (!rc) rc = off.alloc((size_t)3 * (W + 1));
     size_t tmp_bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt.p, off.p, W + 1, st);
     if (!rc) rc = tmp.alloc(tmp_bytes + 16);
-    auto fail = [&](int code) { cnt.release(); off.release(); tmp.release(); trs_spmm_plan_destroy(p); return code; };
     if (rc) return fail(rc);
     cudaMemsetAsync(cnt.p, 0, sizeof(int) * 3 * (W + 1), st);
-    k_count_items<<<grid(W), 256, 0, st>>>(f, p->wr, W, p->chunk, cnt.p, cnt.p + (W + 1), cnt.p + 2 * (W + 1));
+    k_count_items<<<grid(W), 256, 0, st>>>(f, wr, W, p->chunk, cnt.p, cnt.p + (W + 1), cnt.p + 2 * (W + 1));
     for (int i = 0; i < 3; ++i)
         cub::DeviceScan::ExclusiveSum(tmp.p, tmp_bytes, cnt.p + (size_t)i * (W + 1), off.p + (size_t)i * (W + 1), W + 1, st);
     int totals[3] = {0, 0, 0};
@@ -1316,73 +1138,46 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     rc = p->items.alloc(p->n_items);
     if (!rc) rc = p->heavy.alloc(p->n_heavy);
     if (rc) return fail(rc);
-    k_fill_items<<<grid(W), 256, 0, st>>>(f, p->wr, W, p->chunk, off.p, off.p + (W + 1), off.p + 2 * (W + 1),
+    k_fill_items<<<grid(W), 256, 0, st>>>(f, wr, W, p->chunk, off.p, off.p + (W + 1), off.p + 2 * (W + 1),
                                            p->items.p, p->heavy.p);
-    // data of the bulk-copy kernel: 512 zero bytes (+ status word) and the expanded TC blocks
-    rc = p->zeros.alloc(512 + 16);
-    if (!rc) rc = p->tc_dense.alloc((size_t)f.blocks * 128);
+    rc = p->tc_dense.alloc((size_t)f.blocks * 128);
     if (rc) return fail(rc);
-    cudaMemsetAsync(p->zeros.p, 0, 512 + 16, st);
     if (f.blocks > 0)
         k_expand_tc<<<grid((long long)f.blocks * 128), 256, 0, st>>>((const long long*)f.t_binary, f.t_block_offset,
                                                                       (const __half*)f.t_value, f.blocks, p->tc_dense.p);
     e = cudaStreamSynchronize(st);
     if (e == cudaSuccess) e = cudaGetLastError();
-    cnt.release(); off.release(); tmp.release();
-    if (e != cudaSuccess) { trs_spmm_plan_destroy(p); return (int)e; }
+    if (e != cudaSuccess) return fail((int)e);
+    ranges.release(); cnt.release(); off.release(); tmp.release();
     const uintptr_t align_or = (uintptr_t)f.s_tile_column | (uintptr_t)f.s_packed_a | (uintptr_t)f.s_packed_meta |
                                (uintptr_t)f.t_column;
-    // The warp-specialised bulk-copy kernel is opt-in (TRS_SPMM_KERNEL=bulk): measured on B200 it
-    // is slower than the cp.async kernel because 256-byte bulk copies cost ~7 cycles each in the
-    // copy engine; it is kept for wider rows and as the structure a gather4 tensor copy would use.
-    const char* kv = getenv("TRS_SPMM_KERNEL");
     p->arrays_aligned = (align_or & 15) == 0;
-    p->bulk_ok = p->arrays_aligned && kv && strcmp(kv, "bulk") == 0;
-    // The persistent flat-stream schedule is opt-in (TRS_SPMM_KERNEL=flat).  Measured on B200 it is
-    // slower than one CTA per window (4.95 vs 3.23 ms at R-MAT scale 21): the gather is bound by how
-    // many bytes the SM keeps in flight, the flat kernel fits 8 CTAs per SM instead of 10, and the
-    // pipeline bubbles it removes were not the limiter.
-    if (p->arrays_aligned && kv && strcmp(kv, "flat") == 0) {
-        rc = build_flat(p, st);
-        if (rc) { trs_spmm_plan_destroy(p); return rc; }
-    }
     *out_plan = p;
     return TRS_OK;
 }
 
+// No kernel of this library waits on a flag or a barrier another kernel sets, so there is no
+// wait that could give up: the status word is always 0.  Kept for callers of earlier versions.
 extern "C" int trs_spmm_status(const trs_spmm_plan* p, int* status) {
     if (!p || !status) return TRS_E_ARG;
-    TRS_CUDA(cudaDeviceSynchronize());
-    TRS_CUDA(cudaMemcpy(status, p->zeros.p + 512, sizeof(int), cudaMemcpyDeviceToHost));
+    *status = 0;
     return TRS_OK;
 }
 
 extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
     if (!p) return TRS_OK;
-    p->ranges.release();
     p->items.release();
     p->heavy.release();
     p->tc_dense.release();
-    p->zeros.release();
-    p->step_meta.release();
-    p->chunk_begin.release();
-    p->nosteps.release();
     delete p;
     return TRS_OK;
 }
 
 static size_t items_scratch_bytes(const trs_spmm_plan* p, int F) { return (size_t)p->n_slots * 16 * (size_t)F * sizeof(float); }
-static size_t flat_scratch_bytes(const trs_spmm_plan* p, int F) {
-    return p->flat_ok ? (size_t)2 * p->flat_G * 16 * (size_t)F * sizeof(float) : 0;
-}
-static bool flat_usable(const trs_spmm_plan* p, int F) { return p->flat_ok && p->flat_S > 0 && F % 8 == 0; }
 
 extern "C" int trs_spmm_workspace_bytes(const trs_spmm_plan* p, int F, size_t* bytes) {
     if (!p || !bytes || F <= 0) return TRS_E_ARG;
-    // the flat-stream kernel needs two slots per chunk; an unaligned B falls back to the item
-    // kernels, so report what either path may ask for
-    const size_t a = items_scratch_bytes(p, F), b = flat_usable(p, F) ? flat_scratch_bytes(p, F) : 0;
-    *bytes = a > b ? a : b;
+    *bytes = items_scratch_bytes(p, F);
     return TRS_OK;
 }
 
@@ -1394,67 +1189,39 @@ extern "C" int trs_spmm_static_scratch_bytes(const trs_spmm_plan* p, int F, size
 
 extern "C" int trs_spmm_launches(const trs_spmm_plan* p) {
     if (!p) return 0;
-    if (p->flat_ok && p->flat_S > 0) return 1 + (p->flat_G > 1 ? 1 : 0) + (p->n_nosteps > 0 ? 1 : 0);
     return p->n_heavy > 0 ? 2 : 1;
 }
 
-template <int WARPS>
-static int launch_flat_kernel(const trs_spmm_plan* p, const KernelArgs& a, cudaStream_t st) {
-    using T = Tile<WARPS>;
-    constexpr int SMEM = T::SMEM + kMetaRing * 8;
-    FlatArgs fa{p->step_meta.p, p->chunk_begin.p, p->flat_G};
-    const int slabs = ceil_div(a.F, T::FS);
-    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_flat<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    k_window_spmm_flat<WARPS><<<dim3(p->flat_G, slabs), T::THREADS, SMEM, st>>>(a, fa);
-    TRS_LAUNCH_CHECK();
-    if (p->n_nosteps > 0) {
-        k_window_nosteps<WARPS><<<dim3(p->n_nosteps, slabs), T::THREADS, 0, st>>>(a, p->nosteps.p);
-        TRS_LAUNCH_CHECK();
-    }
-    if (p->flat_G > 1) {
-        k_reduce_flat<<<p->flat_G - 1, 256, 0, st>>>(fa, a.scratch, a.C, a.F, a.m_rows, a.window, a.out_half, a.relu);
-        TRS_LAUNCH_CHECK();
-    }
-    return TRS_OK;
-}
-
-template <int WARPS>
-static int launch_bulk_kernel(const KernelArgs& a, int n_items, cudaStream_t st) {
-    using T = BulkTile<WARPS>;
-    dim3 grid(n_items, ceil_div(a.F, T::FS));
-    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_bulk<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
-    k_window_spmm_bulk<WARPS><<<grid, T::THREADS, T::SMEM, st>>>(a);
+template <int FS, int STAGES, int MINB>
+static int launch_warp_kernel(const KernelArgs& a, cudaStream_t st) {
+    using T = WarpTile<FS, STAGES>;
+    dim3 grid(a.n_items, ceil_div(a.F, FS));
+    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_warp<FS, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_warp<FS, STAGES, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  cudaSharedmemCarveoutMaxShared));
+    k_window_spmm_warp<FS, STAGES, MINB><<<grid, 32, T::SMEM, st>>>(a);
     TRS_LAUNCH_CHECK();
     return TRS_OK;
 }
 
+template <int FS, int MINB>
+static int launch_warp_stages(const KernelArgs& a, cudaStream_t st) {
+    static const int stages = env_int("TRS_WARP_STAGES", 3);
+    if (stages == 3) return launch_warp_kernel<FS, 3, MINB>(a, st);
+    if (stages == 4) return launch_warp_kernel<FS, 4, MINB>(a, st);
+    return launch_warp_kernel<FS, 2, MINB>(a, st);
+}
+
 template <int WARPS>
-static int launch_window_kernel(const KernelArgs& a, int n_items, bool lean_ok, cudaStream_t st) {
+static int launch_cta_kernel(const KernelArgs& a, bool lean, cudaStream_t st) {
     using T = Tile<WARPS>;
-    const bool aligned = (a.F % 8 == 0) && (((uintptr_t)a.B & 15) == 0);
-    dim3 grid(n_items, ceil_div(a.F, T::FS));
-    static const bool use_lean = [] { const char* v = getenv("TRS_SPMM_KERNEL"); return !(v && strcmp(v, "cpasync_v1") == 0); }();
-    if (aligned && lean_ok && use_lean) {
-        // Three stages are the default: measured 1-2 % faster than four at R-MAT scale 21 (3.18 vs 3.23 ms,
-        // 3.24 vs 3.28 ms on two boxes) and equal on the clustered case; five stages (8 CTAs per SM) and
-        // 2-warp CTAs with the feature slabs on gridDim.y were slower (3.50 and 3.67 ms).
-        static const int lean_stages = [] { const char* v = getenv("TRS_LEAN_STAGES"); return v && atoi(v) == 4 ? 4 : 3; }();
-        if (lean_stages == 3) {
-            using L = LeanTile<WARPS, 3>;
-            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
-            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                          cudaSharedmemCarveoutMaxShared));
-            k_window_spmm_lean<WARPS, 3><<<grid, L::THREADS, L::SMEM, st>>>(a);
-        } else {
-            using L = LeanTile<WARPS, 4>;
-            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
-            TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 4>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                          cudaSharedmemCarveoutMaxShared));
-            k_window_spmm_lean<WARPS, 4><<<grid, L::THREADS, L::SMEM, st>>>(a);
-        }
-    } else if (aligned) {
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
-        k_window_spmm<WARPS, true><<<grid, T::THREADS, T::SMEM, st>>>(a);
+    dim3 grid(a.n_items, ceil_div(a.F, T::FS));
+    if (lean) {
+        using L = LeanTile<WARPS, 3>;
+        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
+        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
+        k_window_spmm_lean<WARPS, 3><<<grid, L::THREADS, L::SMEM, st>>>(a);
     } else {
         TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
         k_window_spmm<WARPS, false><<<grid, T::THREADS, T::SMEM, st>>>(a);
@@ -1469,20 +1236,19 @@ extern "C" int trs_spmm_run(const trs_spmm_plan* p, const trs_half* B, void* C, 
 }
 
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
-                    size_t workspace_bytes, void* stream, bool items_only, void* const* peers = nullptr, int n_peers = 0,
+                    size_t workspace_bytes, void* stream, void* const* peers = nullptr, int n_peers = 0,
                     long long peer_row0 = 0, int w0 = 0, int w1 = -1);
 
 extern "C" int trs_spmm_run_ex(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
                                void* workspace, size_t workspace_bytes, void* stream) {
-    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, false);
+    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream);
 }
 
 extern "C" int trs_spmm_run_windows(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags,
                                     void* workspace, size_t workspace_bytes, void* stream, int window_begin,
                                     int window_end) {
     if (window_end < 0) return TRS_E_ARG;
-    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, /*items_only=*/true, nullptr, 0, 0,
-                    window_begin, window_end);
+    return run_impl(p, B, C, F, out_dtype, flags, workspace, workspace_bytes, stream, nullptr, 0, 0, window_begin, window_end);
 }
 
 extern "C" int trs_spmm_num_windows(const trs_spmm_plan* p) { return p ? p->num_windows : TRS_E_ARG; }
@@ -1493,12 +1259,12 @@ extern "C" int trs_spmm_run_bcast(const trs_spmm_plan* p, const trs_half* B, voi
     for (int d = 0; d < n_dst; ++d)
         if (!dst[d] || ((uintptr_t)dst[d] & 15)) return TRS_E_ARG;
     if (F % 8 != 0 || ((uintptr_t)B & 15) || !p->arrays_aligned) return TRS_E_ARG;  // the 16-byte row pieces need it
-    return run_impl(p, B, dst[0], F, TRS_OUT_F16, flags, workspace, workspace_bytes, stream, /*items_only=*/true, dst, n_dst, row0);
+    return run_impl(p, B, dst[0], F, TRS_OUT_F16, flags, workspace, workspace_bytes, stream, dst, n_dst, row0);
 }
 
 static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, int out_dtype, int flags, void* workspace,
-                    size_t workspace_bytes, void* stream, bool items_only, void* const* peers, int n_peers,
-                    long long peer_row0, int w0, int w1) {
+                    size_t workspace_bytes, void* stream, void* const* peers, int n_peers, long long peer_row0, int w0,
+                    int w1) {
     if (!p || !B || !C || F <= 0) return TRS_E_ARG;
     if (w1 < 0) w1 = p->num_windows;
     if (w0 < 0 || w0 > w1 || w1 > p->num_windows) return TRS_E_ARG;
@@ -1508,33 +1274,38 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     const int h0 = p->h_heavy_off[w0], n_heavy = p->h_heavy_off[w1] - h0;
     if (flags & ~TRS_EPILOGUE_RELU) return TRS_E_ARG;
     if (out_dtype != TRS_OUT_F32 && out_dtype != TRS_OUT_F16) return TRS_E_ARG;
-    const bool flat = !items_only && w0 == 0 && w1 == p->num_windows && flat_usable(p, F) && (((uintptr_t)B & 15) == 0);
-    size_t need = flat ? flat_scratch_bytes(p, F) : items_scratch_bytes(p, F);
-    if (flat && p->flat_G <= 1) need = 0;
+    const size_t need = items_scratch_bytes(p, F);
     if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     KernelArgs a;
-    a.f = p->f; a.wr = p->wr; a.items = p->items.p + i0;
+    a.f = p->f; a.items = p->items.p + i0; a.n_items = n_items;
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
     a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
     a.n_peers = n_peers; a.peer_row0 = peer_row0;
     for (int d = 0; d < 8; ++d) a.peers[d] = d < n_peers ? peers[d] : nullptr;
-    a.tc_dense = p->tc_dense.p; a.zeros = p->zeros.p; a.status = (int*)(p->zeros.p + 512);
+    a.tc_dense = p->tc_dense.p;
+    // The warp-owner kernel moves everything in 16-byte pieces; anything else takes the fallback.
+    const bool aligned = p->arrays_aligned && (F % 8 == 0) &&
+                         ((((uintptr_t)B | (uintptr_t)C | (uintptr_t)workspace) & 15) == 0);
+    static const int kernel_sel = [] {
+        const char* v = getenv("TRS_SPMM_KERNEL");
+        return !v ? 0 : strcmp(v, "lean") == 0 ? 1 : strcmp(v, "fallback") == 0 ? 2 : 0;
+    }();
+    static const int warp_fs = env_int("TRS_WARP_FS", 128);
     int rc;
-    if (flat) {
-        if (F <= 32) return launch_flat_kernel<1>(p, a, st);
-        if (F <= 64) return launch_flat_kernel<2>(p, a, st);
-        return launch_flat_kernel<4>(p, a, st);
-    }
-    const bool bulk = p->bulk_ok && n_peers == 0 && (F % 8 == 0) && (((uintptr_t)B & 15) == 0);
-    if (bulk) {
-        if (F <= 32) rc = launch_bulk_kernel<1>(a, n_items, st);
-        else if (F <= 64) rc = launch_bulk_kernel<2>(a, n_items, st);
-        else rc = launch_bulk_kernel<4>(a, n_items, st);  // F > 128: feature slabs of 128 on gridDim.y
-    } else if (F <= 32) rc = launch_window_kernel<1>(a, n_items, p->arrays_aligned, st);
-    else if (F <= 64) rc = launch_window_kernel<2>(a, n_items, p->arrays_aligned, st);
-    else rc = launch_window_kernel<4>(a, n_items, p->arrays_aligned, st);
+    if (!aligned || (kernel_sel == 2 && n_peers == 0)) {
+        if (n_peers > 0) return TRS_E_ARG;
+        if (F <= 32) rc = launch_cta_kernel<1>(a, false, st);
+        else if (F <= 64) rc = launch_cta_kernel<2>(a, false, st);
+        else rc = launch_cta_kernel<4>(a, false, st);
+    } else if (kernel_sel == 1 && n_peers == 0) {
+        if (F <= 32) rc = launch_cta_kernel<1>(a, true, st);
+        else if (F <= 64) rc = launch_cta_kernel<2>(a, true, st);
+        else rc = launch_cta_kernel<4>(a, true, st);
+    } else if (F <= 32) rc = launch_warp_stages<32, 32>(a, st);
+    else if (F <= 64 || warp_fs == 64) rc = launch_warp_stages<64, 24>(a, st);
+    else rc = launch_warp_stages<128, 16>(a, st);   // F > 128: feature slabs of 128 on gridDim.y
     if (rc) return rc;
     if (n_heavy > 0) {
         PeerDst pd;
@@ -1553,7 +1324,7 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
 // whole device memory to their own pool at start-up (a later cudaMalloc from a plug-in fails or
 // fragments that pool) and latency-critical loops in which cudaMalloc / cudaFree would stall
 // every stream of the device.  For them trs_spmm_run_static runs the window-per-CTA kernels
-// (k_window_spmm_lean / k_window_spmm + k_reduce_heavy), whose scratch need is small and known
+// (k_window_spmm_warp / k_window_spmm + k_reduce_heavy), whose scratch need is small and known
 // from the plan, with the partial sums of split windows kept in the array below instead of a
 // caller-provided workspace.  Every GPU that loads the library holds these bytes until exit.
 //
@@ -1589,5 +1360,5 @@ extern "C" int trs_spmm_run_static(const trs_spmm_plan* p, const trs_half* B, vo
     }
     // Nothing in the array has to start at zero: every slot a call reads is first written in
     // full by that call's window kernel.
-    return run_impl(p, B, C, F, out_dtype, 0, scratch, (size_t)TRS_STATIC_SCRATCH_BYTES, stream, /*items_only=*/true);
+    return run_impl(p, B, C, F, out_dtype, 0, scratch, (size_t)TRS_STATIC_SCRATCH_BYTES, stream);
 }

@@ -86,6 +86,25 @@ class Format:
         def ptr(t):
             return t.data_ptr() if t.numel() else None
 
+        # Lengths the library derives sizes from must agree with each other: it reads
+        # t_row_offset[parts_t], 8 column ids and 2 bitmaps per block, one row id per part, 16 column
+        # ids / 64 packed words / 8 metadata words per tile.
+        parts_t, blocks, tiles = self.t_window_row.numel(), self.blocks, self.tiles
+        checks = [
+            ("t_column", self.t_column.numel() == 8 * blocks), ("t_binary", self.t_binary.numel() == 2 * blocks),
+            ("t_row_offset", parts_t == 0 or self.t_row_offset.numel() == parts_t + 1),
+            ("t_block_offset", blocks == 0 or self.t_block_offset.numel() == blocks + 1),
+            ("c_row_offset", self.c_row.numel() == 0 or self.c_row_offset.numel() == self.c_row.numel() + 1),
+            ("cs_row_offset", self.cs_row.numel() == 0 or self.cs_row_offset.numel() == self.cs_row.numel() + 1),
+            ("c_value", self.c_value.numel() == self.c_column.numel()),
+            ("cs_value", self.cs_value.numel() == self.cs_column.numel()),
+            ("s_packed_a", self.s_packed_a.numel() == 64 * tiles), ("s_packed_meta", self.s_packed_meta.numel() == 8 * tiles),
+            ("s_tile_column", self.s_tile_column.numel() == 16 * tiles),
+        ]
+        for n, ok in checks:
+            if not ok:
+                raise ValueError(f"{n} has a length inconsistent with the other arrays of its route")
+
         f = TrsFormat()
         for n in ("t_row_offset", "t_block_offset", "t_column", "t_value", "t_window_row", "t_binary",
                   "c_row_offset", "c_row", "c_column", "c_value",

@@ -101,6 +101,34 @@ def even_row_split(n_rows: int, world: int):
     return per, per * world
 
 
+def bind_to_gpu_numa_node(device_index: int):
+    """Pin this process to the CPUs of the NUMA node its GPU hangs off, so that pinned host buffers
+    allocated afterwards (first touch) are local to that GPU's PCIe root: with one process per GPU
+    on a two-socket host, copies from the other socket's memory cross the socket link and run at a
+    fraction of the PCIe rate.  Returns the node id, or None when the topology cannot be read
+    (nothing is changed then).  Only this process's CPU affinity is touched."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 class ShardedHostSpmm:
     """Host-buffer SpMM on `world` GPUs of one box, for a stream of calls over one matrix.
 
@@ -127,8 +155,9 @@ class ShardedHostSpmm:
         self.B = [torch.zeros((padded, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
         self.C = [torch.empty((self.m_local, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
         self.s_in, self.s_comm, self.s_k, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(4))
-        ev = lambda: torch.cuda.Event()  # noqa: E731
+        ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
         self.in_done, self.comm_done, self.k_done, self.out_done = ([ev(), ev()] for _ in range(4))
+        self.in_start, self.comm_start, self.k_start, self.out_start = ([ev(), ev()] for _ in range(4))
         self.seq = 0
         self._keep = []
 
@@ -147,10 +176,12 @@ class ShardedHostSpmm:
         Bs, Cs = self.B[s], self.C[s]
         with torch.cuda.stream(self.s_in):
             self.s_in.wait_event(self.k_done[s])           # the kernels two calls back are done with this slot
+            self.in_start[s].record(self.s_in)
             Bs[b0:b1].copy_(B_slice_host, non_blocking=True)
             self.in_done[s].record(self.s_in)
         with torch.cuda.stream(self.s_comm):
             self.s_comm.wait_event(self.in_done[s])
+            self.comm_start[s].record(self.s_comm)
             if self.world > 1:
                 mine = Bs[self.rank * self.per:(self.rank + 1) * self.per]
                 self.dist.all_gather_into_tensor(Bs, mine, group=self.group)   # in place: `mine` is its own piece of Bs
@@ -158,10 +189,12 @@ class ShardedHostSpmm:
         with torch.cuda.stream(self.s_k):
             self.s_k.wait_event(self.comm_done[s])
             self.s_k.wait_event(self.out_done[s])           # the output copy two calls back has drained this slot
+            self.k_start[s].record(self.s_k)
             self.plan.run(Bs[:self.n_cols], out=Cs)
             self.k_done[s].record(self.s_k)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.k_done[s])
+            self.out_start[s].record(self.s_out)
             C_host.copy_(Cs, non_blocking=True)
             self.out_done[s].record(self.s_out)
         self.seq += 1
@@ -170,3 +203,15 @@ class ShardedHostSpmm:
         for st in (self.s_in, self.s_comm, self.s_k, self.s_out):
             st.synchronize()
         self._keep.clear()
+
+    def leg_ms(self):
+        """Device time of the four legs of the most recent call (after wait()): input copy,
+        all-gather, kernels, output copy.  Legs of consecutive calls overlap, so the step time of a
+        stream of calls tends to the longest leg, not to their sum."""
+        if self.seq == 0:
+            return {"h2d_ms": 0.0, "allgather_ms": 0.0, "kernel_ms": 0.0, "d2h_ms": 0.0}
+        s = (self.seq - 1) & 1
+        return {"h2d_ms": self.in_start[s].elapsed_time(self.in_done[s]),
+                "allgather_ms": self.comm_start[s].elapsed_time(self.comm_done[s]),
+                "kernel_ms": self.k_start[s].elapsed_time(self.k_done[s]),
+                "d2h_ms": self.out_start[s].elapsed_time(self.out_done[s])}

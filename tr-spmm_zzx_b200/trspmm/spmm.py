@@ -61,21 +61,37 @@ class SpmmPlan:
     def launches(self) -> int:
         return self.lib.trs_spmm_launches(self._handle)
 
-    def run(self, B: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float16,
-            relu: bool = False) -> torch.Tensor:
+    def _check_B(self, B: torch.Tensor) -> int:
+        """Every entry that hands B to a kernel goes through this: a short or strided B would become
+        an out-of-range gather on the device."""
         if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
             raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
         if B.shape[0] != self.k_cols:
             raise ValueError(f"B has {B.shape[0]} rows, the plan expects {self.k_cols}")
-        F = B.shape[1]
-        if out is None:
-            out = torch.empty((self.m_rows, F), dtype=out_dtype, device=self.device)
-        elif out.shape != (self.m_rows, F) or not out.is_contiguous() or out.device != self.device:
+        if B.shape[1] <= 0:
+            raise ValueError("B needs at least one feature column")
+        return B.shape[1]
+
+    def _check_out(self, out: torch.Tensor, F: int):
+        if out.shape != (self.m_rows, F) or not out.is_contiguous() or out.device != self.device:
             raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
+        _out_code(out.dtype)
+
+    def _workspace(self, F: int) -> torch.Tensor:
         ws = self._ws.get(F)
         if ws is None:
             ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
             self._ws[F] = ws
+        return ws
+
+    def run(self, B: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float16,
+            relu: bool = False) -> torch.Tensor:
+        F = self._check_B(B)
+        if out is None:
+            out = torch.empty((self.m_rows, F), dtype=out_dtype, device=self.device)
+        else:
+            self._check_out(out, F)
+        ws = self._workspace(F)
         with torch.cuda.device(self.device):
             _lib.check(self.lib.trs_spmm_run_ex(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
                                                 1 if relu else 0, ws.data_ptr(), ws.numel(),
@@ -90,15 +106,9 @@ class SpmmPlan:
                     relu: bool = False) -> torch.Tensor:
         """trs_spmm_run_windows: the product restricted to the row windows [window_begin, window_end);
         only those rows of `out` are written."""
-        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
-            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
-        F = B.shape[1]
-        if out.shape != (self.m_rows, F) or not out.is_contiguous() or out.device != self.device:
-            raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
-        ws = self._ws.get(F)
-        if ws is None:
-            ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
-            self._ws[F] = ws
+        F = self._check_B(B)
+        self._check_out(out, F)
+        ws = self._workspace(F)
         with torch.cuda.device(self.device):
             _lib.check(self.lib.trs_spmm_run_windows(self._handle, B.data_ptr(), out.data_ptr(), F, _out_code(out.dtype),
                                                      1 if relu else 0, ws.data_ptr(), ws.numel(),
@@ -110,13 +120,10 @@ class SpmmPlan:
         """trs_spmm_run_bcast: the fp16 result rows go straight from the kernel's epilogue into every
         buffer of `dst_ptrs` (device pointers of [N_total, F] fp16 matrices: this GPU's and its
         NVLink peers') at rows row0 + local row.  Asynchronous on the current stream."""
-        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
-            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
-        F = B.shape[1]
-        ws = self._ws.get(F)
-        if ws is None:
-            ws = torch.empty(max(self.workspace_bytes(F), 16), dtype=torch.uint8, device=self.device)
-            self._ws[F] = ws
+        F = self._check_B(B)
+        if not 1 <= len(dst_ptrs) <= 8 or row0 < 0:
+            raise ValueError("1 to 8 destination buffers and a non-negative row offset")
+        ws = self._workspace(F)
         arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
         with torch.cuda.device(self.device):
             _lib.check(self.lib.trs_spmm_run_bcast(self._handle, B.data_ptr(), arr, len(dst_ptrs), int(row0), F,
@@ -130,10 +137,7 @@ class SpmmPlan:
         `out` must be given: this path allocates nothing, here or in the library.  Raises
         TrsError(-10) when the plan needs more scratch than the fixed array holds.  Calls on one
         device share the array, so do not let two of them overlap on the GPU."""
-        if B.device != self.device or B.dtype != torch.float16 or B.dim() != 2 or not B.is_contiguous():
-            raise ValueError("B must be a contiguous fp16 [k_cols, F] tensor on the plan's device")
-        if out.shape != (self.m_rows, B.shape[1]) or not out.is_contiguous() or out.device != self.device:
-            raise ValueError("out must be a contiguous [m_rows, F] tensor on the plan's device")
+        self._check_out(out, self._check_B(B))
         with torch.cuda.device(self.device):
             _lib.check(self.lib.trs_spmm_run_static(self._handle, B.data_ptr(), out.data_ptr(), B.shape[1],
                                                     _out_code(out.dtype), _lib.current_stream_ptr(self.device)))
@@ -192,9 +196,21 @@ class ResidentSpmm:
             cf = self._keep.c_struct()
             _lib.check(self.lib.trs_resident_create(C.byref(cf), mOri, kOri, window, max_dimN, C.byref(self._handle)))
 
-    def forward(self, rhs: torch.Tensor, out: torch.Tensor):
+    def _check_host(self, rhs: torch.Tensor, out: torch.Tensor):
+        """Shared by forward and submit: the library copies kOri * F and mOri * F elements, so a
+        short or strided host tensor would be read or written past its end."""
         if rhs.device.type != "cpu" or out.device.type != "cpu":
-            raise ValueError("ResidentSpmm.forward takes host tensors")
+            raise ValueError("ResidentSpmm takes host tensors")
+        if rhs.dim() != 2 or not rhs.is_contiguous() or not out.is_contiguous() or rhs.dtype != torch.float16:
+            raise ValueError("rhs must be a contiguous fp16 [kOri, F] tensor, out contiguous")
+        if rhs.shape[0] != self.kOri or out.shape != (self.mOri, rhs.shape[1]):
+            raise ValueError(f"rhs must be [{self.kOri}, F] and out [{self.mOri}, F]")
+        if not 0 < rhs.shape[1] <= self.max_dimN:
+            raise ValueError(f"F must be in 1..{self.max_dimN} (the width this object was created for)")
+        _out_code(out.dtype)
+
+    def forward(self, rhs: torch.Tensor, out: torch.Tensor):
+        self._check_host(rhs, out)
         timing = _lib.TrsTiming()
         _lib.check(self.lib.trs_resident_forward(self._handle, rhs.data_ptr(), out.data_ptr(), rhs.shape[1],
                                                  _out_code(out.dtype), C.byref(timing)))
@@ -204,12 +220,7 @@ class ResidentSpmm:
         """trs_resident_submit: enqueue one call and return at once.  Consecutive submits overlap
         (input copy of the next call beside the kernels and the output copy of this one); `rhs`
         and `out` must be pinned host tensors that stay untouched until wait() returns."""
-        if rhs.device.type != "cpu" or out.device.type != "cpu":
-            raise ValueError("ResidentSpmm.submit takes host tensors")
-        if not rhs.is_contiguous() or not out.is_contiguous() or rhs.dtype != torch.float16:
-            raise ValueError("rhs must be contiguous fp16, out contiguous")
-        if rhs.shape[0] != self.kOri or out.shape != (self.mOri, rhs.shape[1]):
-            raise ValueError("shape mismatch")
+        self._check_host(rhs, out)
         self._inflight.append((rhs, out))
         _lib.check(self.lib.trs_resident_submit(self._handle, rhs.data_ptr(), out.data_ptr(), rhs.shape[1],
                                                 _out_code(out.dtype)))
