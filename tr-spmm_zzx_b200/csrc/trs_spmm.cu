@@ -19,6 +19,7 @@
 // mGCNkernel_online.cu:1589-1590, 1689-1712).  Heavy windows are cut into several items that
 // write fp32 partial sums to scratch; a second kernel adds them in a fixed order, so results are
 // bit-identical from run to run.
+#include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 
 #include <string.h>
@@ -155,6 +156,15 @@ __global__ void k_check_range(const int* __restrict__ a, long long n, int lo, in
     int v = a[i];
     if (v < lo || v >= hi) atomicOr(err, bit);
 }
+// Launch-order class of an item: long items first, so that the last wave of the grid consists of
+// short ones (one item per warp: a long item that starts late would keep its SM busy alone).
+__global__ void k_item_class(const Item* __restrict__ items, int n, unsigned char* __restrict__ cls) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int steps = items[i].step_end - items[i].step_begin;
+    cls[i] = steps >= 192 ? 0 : steps >= 96 ? 1 : steps >= 48 ? 2 : 3;
+}
+
 // The TC kernels read t_value[t_block_offset[b] + rank] with rank taken from the block's two
 // bitmaps, so the bitmaps' population must equal the block's share of t_value.
 __global__ void k_check_tc_popcount(const long long* __restrict__ t_binary, const int* __restrict__ t_block_offset,
@@ -657,13 +667,16 @@ struct WarpTile {
 
 // Adds the item's CSR remainder parts into a zeroed 16 x FS fp32 tile in shared memory.  A group
 // of FS / 8 lanes reads one B row segment with 16-byte loads; the 32 / (FS / 8) groups of the warp
-// take different entries of the part and their partial sums meet in a shuffle reduction.
+// take different entries of the part and their partial sums meet in a shuffle reduction.  The
+// part headers (row, entry range) are read 32 parts at a time and the column ids and values 32
+// entries at a time, one per lane, and handed round with shuffles, so that the only dependent
+// loads left in the loop are the B-row gathers themselves, four of them in flight per lane.
 template <int FS>
 __device__ __forceinline__ void csr_parts_to_tile(const Item& it, const KernelArgs& a, int fbase, int lane, float* tile) {
     constexpr int LPR = FS / 8, G = 32 / LPR, PITCH = FS + 4;  // floats
+    constexpr int U = 4;                                       // B-row loads in flight per lane
     const int grp = lane / LPR, ch = lane % LPR;
-    const int f = fbase + ch * 8;
-    const bool fin = f < a.F;
+    const bool fin = fbase + ch * 8 < a.F;
     const uint4* Bq = (const uint4*)a.B;
     const uint32_t pitch16 = (uint32_t)a.F >> 3;
     const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;
@@ -674,38 +687,66 @@ __device__ __forceinline__ void csr_parts_to_tile(const Item& it, const KernelAr
         const int* rrow = pass ? a.f.cs_row : a.f.c_row;
         const int* rcol = pass ? a.f.cs_column : a.f.c_column;
         const __half* rval = (const __half*)(pass ? a.f.cs_value : a.f.c_value);
-        for (int p = pb; p < pe; ++p) {
-            const int lr = __ldg(rrow + p) - it.window * a.window;
-            const int e0 = __ldg(roff + p), e1 = __ldg(roff + p + 1);
-            float s[8];
+        for (int p0 = pb; p0 < pe; p0 += 32) {
+            const int np = min(32, pe - p0);
+            int h_row = 0, h_e0 = 0, h_e1 = 0;
+            if (lane < np) {
+                h_row = __ldg(rrow + p0 + lane) - it.window * a.window;
+                h_e0 = __ldg(roff + p0 + lane);
+                h_e1 = __ldg(roff + p0 + lane + 1);
+            }
+            for (int pi = 0; pi < np; ++pi) {
+                const int lr = __shfl_sync(0xffffffffu, h_row, pi);
+                const int e0 = __shfl_sync(0xffffffffu, h_e0, pi);
+                const int e1 = __shfl_sync(0xffffffffu, h_e1, pi);
+                float s[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) s[i] = 0.f;
-            for (int e = e0 + grp; e < e1; e += G) {
-                const int c = __ldg(rcol + e);
-                const float v = __half2float(__ldg(rval + e));
-                if (fin) {
-                    const uint4 q = __ldg(Bq + (size_t)((uint32_t)c * pitch16 + chunk16));
-                    const __half2* h = (const __half2*)&q;
+                for (int i = 0; i < 8; ++i) s[i] = 0.f;
+                for (int eb = e0; eb < e1; eb += 32) {
+                    const int cnt = min(32, e1 - eb);
+                    int my_c = 0;
+                    float my_v = 0.f;
+                    if (lane < cnt) {
+                        my_c = __ldg(rcol + eb + lane);
+                        my_v = __half2float(__ldg(rval + eb + lane));
+                    }
+                    for (int i0 = 0; i0 < cnt; i0 += G * U) {
+                        uint4 q[U];
+                        float v[U];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 x = __half22float2(h[i]);
-                        s[2 * i] = fmaf(v, x.x, s[2 * i]);
-                        s[2 * i + 1] = fmaf(v, x.y, s[2 * i + 1]);
+                        for (int u = 0; u < U; ++u) {
+                            const int idx = i0 + grp + G * u;
+                            const int c = __shfl_sync(0xffffffffu, my_c, idx & 31);
+                            v[u] = __shfl_sync(0xffffffffu, my_v, idx & 31);
+                            q[u] = make_uint4(0u, 0u, 0u, 0u);
+                            if (idx < cnt && fin) q[u] = __ldg(Bq + (size_t)((uint32_t)c * pitch16 + chunk16));
+                            else v[u] = 0.f;
+                        }
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const __half2* h = (const __half2*)&q[u];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 x = __half22float2(h[i]);
+                                s[2 * i] = fmaf(v[u], x.x, s[2 * i]);
+                                s[2 * i + 1] = fmaf(v[u], x.y, s[2 * i + 1]);
+                            }
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int off = LPR; off < 32; off <<= 1)
+                for (int off = LPR; off < 32; off <<= 1)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], off);
-            if (grp == 0 && lr >= 0 && lr < 16) {
-                float4* d = (float4*)(tile + lr * PITCH + ch * 8);
-                float4 u = d[0], w = d[1];
-                u.x += s[0]; u.y += s[1]; u.z += s[2]; u.w += s[3];
-                w.x += s[4]; w.y += s[5]; w.z += s[6]; w.w += s[7];
-                d[0] = u; d[1] = w;
+                    for (int i = 0; i < 8; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], off);
+                if (grp == 0 && lr >= 0 && lr < 16) {
+                    float4* d = (float4*)(tile + lr * PITCH + ch * 8);
+                    float4 u = d[0], w = d[1];
+                    u.x += s[0]; u.y += s[1]; u.z += s[2]; u.w += s[3];
+                    w.x += s[4]; w.y += s[5]; w.z += s[6]; w.w += s[7];
+                    d[0] = u; d[1] = w;
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
     }
 }
@@ -987,7 +1028,8 @@ using namespace trs;
 struct trs_spmm_plan {
     trs_format f;
     int m_rows, k_cols, window, num_windows, chunk;
-    DevBuf<Item> items;
+    DevBuf<Item> items;               // in window order (window-range runs index it by window)
+    DevBuf<Item> items_sorted;        // the same items, long ones first (whole-matrix runs)
     DevBuf<Heavy> heavy;
     DevBuf<__half> tc_dense;          // TC blocks expanded to dense 16 x 8 fp16 tiles
     int n_items, n_heavy, n_slots;
@@ -1140,6 +1182,24 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     if (rc) return fail(rc);
     k_fill_items<<<grid(W), 256, 0, st>>>(f, wr, W, p->chunk, off.p, off.p + (W + 1), off.p + 2 * (W + 1),
                                            p->items.p, p->heavy.p);
+    // launch order of whole-matrix runs: a stable sort by length class (window order inside a class)
+    if (p->n_items > 0) {
+        DevBuf<unsigned char> cls, cls_out, sort_tmp;
+        rc = p->items_sorted.alloc(p->n_items);
+        if (!rc) rc = cls.alloc(p->n_items);
+        if (!rc) rc = cls_out.alloc(p->n_items);
+        size_t sort_bytes = 0;
+        cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, cls.p, cls_out.p, p->items.p, p->items_sorted.p, p->n_items, 0, 2, st);
+        if (!rc) rc = sort_tmp.alloc(sort_bytes + 16);
+        if (!rc) {
+            k_item_class<<<grid(p->n_items), 256, 0, st>>>(p->items.p, p->n_items, cls.p);
+            cub::DeviceRadixSort::SortPairs(sort_tmp.p, sort_bytes, cls.p, cls_out.p, p->items.p, p->items_sorted.p, p->n_items, 0, 2, st);
+            e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) rc = (int)e;
+        }
+        cls.release(); cls_out.release(); sort_tmp.release();
+        if (rc) return fail(rc);
+    }
     rc = p->tc_dense.alloc((size_t)f.blocks * 128);
     if (rc) return fail(rc);
     if (f.blocks > 0)
@@ -1156,8 +1216,9 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     return TRS_OK;
 }
 
-// No kernel of this library waits on a flag or a barrier another kernel sets, so there is no
-// wait that could give up: the status word is always 0.  Kept for callers of earlier versions.
+// No kernel of this library waits on a flag or a barrier that another warp or kernel sets (the
+// window kernels synchronise inside one warp or one CTA only), so there is no wait that could
+// give up: the status word is always 0.  Kept for callers of earlier versions.
 extern "C" int trs_spmm_status(const trs_spmm_plan* p, int* status) {
     if (!p || !status) return TRS_E_ARG;
     *status = 0;
@@ -1167,6 +1228,7 @@ extern "C" int trs_spmm_status(const trs_spmm_plan* p, int* status) {
 extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
     if (!p) return TRS_OK;
     p->items.release();
+    p->items_sorted.release();
     p->heavy.release();
     p->tc_dense.release();
     delete p;
@@ -1278,7 +1340,8 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     if (need > 0 && (!workspace || workspace_bytes < need)) return TRS_E_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     KernelArgs a;
-    a.f = p->f; a.items = p->items.p + i0; a.n_items = n_items;
+    a.f = p->f; a.n_items = n_items;
+    a.items = (w0 == 0 && w1 == p->num_windows) ? p->items_sorted.p : p->items.p + i0;
     a.B = (const __half*)B; a.C = C; a.scratch = (float*)workspace;
     a.m_rows = p->m_rows; a.k_cols = p->k_cols; a.window = p->window; a.F = F; a.out_half = out_dtype == TRS_OUT_F16;
     a.relu = (flags & TRS_EPILOGUE_RELU) ? 1 : 0;
