@@ -146,8 +146,7 @@ def make_matrix(workload, device):
 # DRAM bytes of one launch of the window kernel on one GPU (dram__bytes_read.sum +
 # dram__bytes_write.sum of single-metric, one-pass ncu captures of this very command; the
 # summaries under profiles/ give the commands).  Workloads not captured report null.
-MEASURED_TRAFFIC = {("rmat21", 128): 8.29e9 + 0.628e9, ("rmat20", 128): 1.728e9 + 0.269e9,
-                    ("clustered", 128): 273.9e6 + 55.9e6}
+MEASURED_TRAFFIC = {("rmat21", 128): 8.177e9 + 0.616e9, ("rmat20", 128): 1.664e9 + 0.2575e9}
 
 
 def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):
@@ -618,29 +617,47 @@ def run_build(args):
     dev = torch.device("cuda", 0)
     rp, col, val, _ = make_matrix(args.workload, dev)
     n, nnz = rp.numel() - 1, col.numel()
+    from trspmm.builder import arena_bytes
     steps = max(1, min(args.steps, 10))
+    # headline: trs_build_fill into a caller-owned arena sized once by trs_build_query (the call allocates nothing)
+    arena = torch.empty(arena_bytes(n, nnz), dtype=torch.uint8, device=dev)
     for _ in range(min(args.warmup, 3)):
-        fmt, st = build_format(rp, col, val)
+        fmt, st = build_format(rp, col, val, arena=arena)
         del fmt
     torch.cuda.synchronize()
     with ClockSampler(0) as clocks:
         t0 = time.perf_counter()
         kernel_ms = 0.0
         for _ in range(steps):
-            fmt, st = build_format(rp, col, val)
+            fmt, st = build_format(rp, col, val, arena=arena)
             kernel_ms += st["build_ms"]
             out_bytes = sum(a.numel() * a.element_size() for a in fmt.arrays())
             del fmt
         torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) * 1e3 / steps
+    arena_used = st["arena_used"]
+    del arena
+    torch.cuda.empty_cache()
+    # beside it: trs_build_create, which allocates outputs and temporaries itself on every call
+    fmt, _ = build_format(rp, col, val)
+    del fmt
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(min(steps, 3)):
+        fmt, _ = build_format(rp, col, val)
+        del fmt
+    torch.cuda.synchronize()
+    ms_create = (time.perf_counter() - t0) * 1e3 / min(steps, 3)
     peak, src = peaks()
     alg = nnz * 12 + (n + 1) * 4 + out_bytes   # CSR in (i32 column, f32 value, row pointers... read once) + every array written once
     line = {"metric": "format build M nnz/s", "value": nnz / (ms * 1e-3) / 1e6, "unit": "Mnnz/s", "n_gpus": 1,
             "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "dtype": "i32 / u8 / f32->f16", "data": "synthetic",
             "config": {"workload": args.workload, "op": "build", "n_rows": n, "nnz": nnz,
-                       "call": "trs_build_create (wall time, includes its device allocations)",
+                       "call": "trs_build_fill into a caller-owned arena (wall time; no allocation inside the call)",
                        "device_ms_per_build": kernel_ms / steps, "output_bytes": out_bytes,
+                       "arena_bytes_query": arena_bytes(n, nnz), "arena_bytes_used": arena_used,
+                       "ms_per_step_trs_build_create": ms_create,
                        "groups": st["groups"], "tiles": st["tiles"], "tc_blocks": st["tc_blocks"]},
             "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None,
@@ -766,7 +783,7 @@ def main():
                     help="spmm: lossless format (no dropped entries; value counts all nnz) - a separate, labelled configuration")
     ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn", "build", "match24"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
-    ap.add_argument("--gather", default="h1", choices=["h1", "z2", "fused"], help="gcn: which matrix the ranks exchange")
+    ap.add_argument("--gather", default="push", choices=["h1", "z2", "fused", "push"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -229,6 +229,20 @@ typedef struct trs_builder trs_builder; /* opaque; owns the output arrays on the
 int trs_build_create(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
                      const trs_build_config* cfg, void* stream, trs_builder** out);
 int trs_build_destroy(trs_builder* b);
+/* The same build with every byte of device memory owned by the caller (the reference allocates
+ * its outputs itself, block_online.cpp:844-870; a host that pools its device memory cannot let a
+ * plug-in call cudaMalloc): trs_build_query gives an upper bound of the arena one build needs from
+ * the matrix sizes alone; trs_build_fill builds with outputs and temporaries cut out of `arena`
+ * (256-byte aligned device memory) and calls neither cudaMalloc nor cudaFree.  The builder it
+ * returns points into the arena: the arrays stay valid until the caller reuses that memory;
+ * trs_build_destroy frees only the small host object.  TRS_E_WORKSPACE when the arena is too small
+ * (nothing is left half-built).  trs_build_arena_used reports the high-water mark of a finished
+ * build, so that a caller building many matrices of one shape can size the arena from the first. */
+int trs_build_query(int n_rows, long long nnz, const trs_build_config* cfg, size_t* arena_bytes);
+int trs_build_fill(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
+                   const trs_build_config* cfg, void* arena, size_t arena_bytes, void* stream,
+                   trs_builder** out);
+int trs_build_arena_used(const trs_builder* b, size_t* bytes);
 /* element counts of the 29 arrays, in the reference's return order */
 int trs_build_sizes(const trs_builder* b, long long sizes[TRS_BUILD_NUM_ARRAYS]);
 int trs_build_stats(const trs_builder* b, trs_build_stats_t* stats);
@@ -248,7 +262,12 @@ int trs_debug_stdsort_order(const unsigned char* keys, int n, int* out, int* hea
  *   variant 0  matching_utils.match_2to4             (block_matching_window_para_dr.cpp:361-449)
  *   variant 1  matching_utils_hash.match_2to4_hash   (block_matching_hash.cpp:373-441)
  *   variant 2  matching_utils_bucket.match_2to4_bucket (block_matching_bucket.cpp:430-499)
- * dense_threshold / t_max are used by variant 0 only (the others fix their thresholds). */
+ *   variant 3  matching_utils_online.match_2to4_online (block_matching_online.cu:85-431, 554-649):
+ *              the reference builds the window's column list in the slot order of a 2048-entry
+ *              open-addressing table filled by racing threads; this is its result for the
+ *              schedule in which the rows of a window insert one after the other (window = 16,
+ *              columns beyond the 2048th distinct one of a window are lost, as in the reference)
+ * dense_threshold / t_max are used by variants 0 and 3 only (the others fix their thresholds). */
 typedef struct trs_match_stats {
     int32_t total_rows, total_cols;
     long long total_nnz;
@@ -260,6 +279,7 @@ typedef struct trs_match_stats {
     long long tc_total_nnz, tc_block_count; /* variant 0 only */
     int32_t tc_block_max_nnz, tc_block_min_nnz;
     long long fake_zeros_exact; /* variant 1: 2*rows*groups - nnz, the per-row count block_match_cuda.cu:260-280 makes */
+    long long dense_to_tc_cols, dense_to_sptc_cols; /* variants 0 and 3: pooled columns routed to TC blocks / fallback groups */
 } trs_match_stats;
 int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, int n_rows, int window,
                       int dense_threshold, int t_max, void* stream, trs_match_stats* out);

@@ -27,7 +27,7 @@ def main():
     W2 = (torch.randn(128, 64, generator=g) * 0.02).half().to(dev)
     rp, col, val = rp.to(dev), col.to(dev), val.to(dev)
     ok = True
-    for gather in ("h1", "z2", "fused"):
+    for gather in ("h1", "z2", "fused", "push"):
         model = ShardedGCN2(rp, col, val, rank, world)
         mine = model.forward(X, W1, W2, gather=gather)
         full = torch.zeros(n, 64, dtype=torch.float16, device=dev)

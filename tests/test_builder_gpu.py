@@ -193,3 +193,34 @@ def test_strict_mode_is_lossless(case):
     B = torch.randn(n, 64, generator=torch.Generator().manual_seed(0)).half()
     out = SpmmPlan(strict, n, n).run(B.cuda(), out_dtype=torch.float32).cpu()
     assert O.scaled_max_error(out, O.spmm_csr(rp, col, val, B)) <= 2e-5
+
+
+def test_builder_with_caller_owned_arena():
+    """trs_build_query / trs_build_fill: the same 29 arrays with every device byte cut out of a
+    caller-provided arena (no cudaMalloc inside the call); a short arena is refused cleanly and a
+    second build reuses the same memory."""
+    from trspmm import TrsError
+    from trspmm.builder import arena_bytes
+    for strict in (False, True):
+        rp, col, val = graphs.rmat_graph(13, 16, seed=21)
+        want, stats0 = build_format(rp.cuda(), col.cuda(), val.cuda(), strict=strict)
+        need = arena_bytes(rp.numel() - 1, col.numel(), strict=strict)
+        arena = torch.empty(need + 300, dtype=torch.uint8, device="cuda")[7:]   # deliberately unaligned start
+        for _ in range(2):
+            fmt, stats = build_format(rp.cuda(), col.cuda(), val.cuda(), strict=strict, arena=arena)
+            for n, a, b in zip(O.FORMAT_NAMES, fmt.arrays(), want.arrays()):
+                assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b), n
+                if a.numel():
+                    assert arena.data_ptr() <= a.data_ptr() < arena.data_ptr() + arena.numel(), n
+            assert 0 < stats["arena_used"] <= need
+            assert stats["dropped_nnz"] == stats0["dropped_nnz"]
+        small = torch.empty(max(stats["arena_used"] // 3, 4096), dtype=torch.uint8, device="cuda")
+        with pytest.raises(TrsError) as e:
+            build_format(rp.cuda(), col.cuda(), val.cuda(), strict=strict, arena=small)
+        assert e.value.code == -7
+    # the empty matrix and the single entry still work
+    rp = torch.zeros(33, dtype=torch.int32)
+    arena = torch.empty(arena_bytes(32, 0), dtype=torch.uint8, device="cuda")
+    fmt, _ = build_format(rp.cuda(), torch.zeros(0, dtype=torch.int32).cuda(), torch.zeros(0).cuda(), arena=arena)
+    want, _ = O.build_format(rp, torch.zeros(0, dtype=torch.int32), torch.zeros(0))
+    _same(fmt, want)

@@ -100,9 +100,53 @@ def test_cuda_and_online_entry_points_keep_the_invariants():
     with pytest.raises(RuntimeError):
         matching_utils_cuda.match_2to4(rp.cuda(), col.cuda(), val.cuda(), window_size=17)
     o = matching_utils_online.match_2to4_online(rp.numpy(), col.numpy(), val.numpy())
+    assert o == matching_utils_online.match_2to4_online(rp.numpy(), col.numpy(), val.numpy())   # deterministic
     assert set(o) == {"total_rows", "total_cols", "total_nnz", "num_sptc_groups", "num_tc_blocks", "dense_to_tc_cols",
                       "dense_to_sptc_cols", "fine_fb", "coarse_fb_cols", "num_16x16_blocks", "block_padding_groups",
                       "fake_zeros"}
     assert o["block_padding_groups"] == o["num_16x16_blocks"] * 4 - o["num_sptc_groups"]
     assert o["dense_to_tc_cols"] == o["num_tc_blocks"] * 8 and o["dense_to_sptc_cols"] >= 0
     assert o["total_nnz"] == nnz
+
+
+def _wide_window_graph(n_rows=48, distinct=2600, seed=4):
+    """A few windows, one of which touches more distinct columns than the 2048 slots of the
+    reference's per-window table (the columns beyond are lost, block_matching_online.cu:163-176),
+    with column ids that collide modulo 2048."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    for r in range(n_rows):
+        if r < 16:
+            cols = rng.choice(6000, size=distinct // 8, replace=False)
+        else:
+            cols = rng.choice(6000, size=int(rng.integers(0, 40)), replace=False)
+        rows.append(np.sort(cols))
+    rp = np.zeros(n_rows + 1, dtype=np.int32)
+    rp[1:] = np.cumsum([len(c) for c in rows])
+    col = np.concatenate(rows).astype(np.int32)
+    return rp, col, np.ones(col.size, dtype=np.float32)
+
+
+@pytest.mark.parametrize("case", ["rmat", "clustered", "uniform_ragged", "wide", "threshold"])
+def test_online_variant_matches_its_cpu_replay(case):
+    """trs_match24_stats variant 3 against oracle.match_online_emulation: the same rules
+    (block_matching_online.cu:85-431) replayed in plain Python for the row-sequential schedule."""
+    import matching_utils_online
+    kw = {}
+    if case == "rmat":
+        rp, col, val = (t.numpy() for t in graphs.rmat_graph(9, 12, seed=3))
+    elif case == "clustered":
+        rp, col, val = (t.numpy() for t in graphs.clustered_graph(n=600, community=64, intra=20, glob=3, seed=2))
+    elif case == "uniform_ragged":
+        rp, col, val = (t.numpy() for t in graphs.uniform_graph(n=333, per_row=7, seed=9))
+    elif case == "wide":
+        rp, col, val = _wide_window_graph()
+    else:
+        rp, col, val = (t.numpy() for t in graphs.rmat_graph(9, 12, seed=5))
+        kw = dict(dense_threshold=4, t_max=2)
+    got = matching_utils_online.match_2to4_online(rp, col, val, **kw)
+    want = O.match_online_emulation(rp, col, **kw)
+    want["fake_zeros"] = ((want["fake_zeros"] + 2 ** 31) % 2 ** 32) - 2 ** 31
+    assert got == want
+    if case == "wide":
+        assert got["total_nnz"] == col.size      # the input count, lost columns included

@@ -65,3 +65,26 @@ def test_reference_call_signature():
     assert nrp.shape == (257,) and ncol.shape == col.shape and sorted(rid.tolist()) == list(range(256))
     import tr_tca_reorder
     assert tr_tca_reorder.apply_tca_reorder is apply_tca_reorder
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("method", METHODS)
+def test_orders_on_the_device_equal_the_cpu_orders_and_feed_the_spmm(method):
+    """The same orders computed on CUDA tensors (the benchmark path): identical permutation, and the
+    SpMM of the re-ordered matrix equals the row-permuted SpMM of the original (lossless format,
+    so that the comparison does not depend on which entries each format drops)."""
+    from trspmm import SpmmPlan, build_format
+    rp, col, val = graphs.rmat_graph(12, 16, seed=8)
+    n = rp.numel() - 1
+    rid_cpu = row_order(rp, col, method, n_cols=n)
+    rid = row_order(rp.cuda(), col.cuda(), method, n_cols=n)
+    assert rid.is_cuda and torch.equal(rid.cpu(), rid_cpu)
+    nrp, ncol, nval = permute_rows(rp.cuda(), col.cuda(), val.cuda(), rid)
+    B = torch.randn(n, 64, generator=torch.Generator().manual_seed(0)).half().cuda()
+    f0, _ = build_format(rp.cuda(), col.cuda(), val.cuda(), strict=True)
+    f1, _ = build_format(nrp, ncol, nval, strict=True)
+    c0 = SpmmPlan(f0, n, n).run(B, out_dtype=torch.float32)
+    c1 = SpmmPlan(f1, n, n).run(B, out_dtype=torch.float32)
+    scale = c0.abs().amax(dim=1, keepdim=True).clamp_min(1e-20)
+    assert float(((c1 - c0[rid]).abs() / scale[rid]).max()) <= 2e-5
+    assert window_column_pairs(nrp, ncol) <= window_column_pairs(rp.cuda(), col.cuda()) or method == "minhash"

@@ -776,6 +776,8 @@ using namespace trs;
 
 struct trs_builder {
     BuildCfg cfg;
+    Arena arena_store;
+    Arena* arena = nullptr;   // set: outputs and scratch come from the caller's memory
     int n_rows = 0, W = 0;
     long long nnz = 0;
     // the 29 arrays, reference order (block_online.cpp:844-870)
@@ -810,20 +812,40 @@ struct trs_builder {
 
 namespace {
 
-struct Scratch {  // frees everything it handed out
+struct Scratch {  // frees everything it handed out (or gives it back to the caller's arena)
+    Arena* arena = nullptr;
     std::vector<void*> ptrs;
-    ~Scratch() { for (void* p : ptrs) cudaFree(p); }
+    std::vector<size_t> bytes;
+    ~Scratch() {
+        for (size_t i = ptrs.size(); i-- > 0;)
+            if (ptrs[i]) {
+                if (arena) arena->give_back(ptrs[i], bytes[i]);
+                else cudaFree(ptrs[i]);
+            }
+    }
     template <class T>
     int get(size_t n, T** out) {
         void* d = nullptr;
-        cudaError_t e = cudaMalloc(&d, (n ? n : 1) * sizeof(T));
-        if (e != cudaSuccess) { *out = nullptr; return (int)e; }
+        const size_t nb = (n ? n : 1) * sizeof(T);
+        if (arena) {
+            d = arena->take(nb);
+            if (!d) { *out = nullptr; return TRS_E_WORKSPACE; }
+        } else {
+            cudaError_t e = cudaMalloc(&d, nb);
+            if (e != cudaSuccess) { *out = nullptr; return (int)e; }
+        }
         ptrs.push_back(d);
+        bytes.push_back(nb);
         *out = (T*)d;
         return 0;
     }
     void drop(void* p) {
-        for (auto& q : ptrs) if (q == p) { cudaFree(p); q = nullptr; }
+        for (size_t i = 0; i < ptrs.size(); ++i)
+            if (ptrs[i] == p) {
+                if (arena) arena->give_back(p, bytes[i]);
+                else cudaFree(p);
+                ptrs[i] = nullptr;
+            }
     }
 };
 
@@ -904,6 +926,7 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     const int n = B->n_rows, window = cfg.window;
     const int W = B->W;
     Scratch sc;
+    sc.arena = B->arena;
     Cub cub_(sc, st);
     int* d_err;
     TRS_TRY(sc.get<int>(4, &d_err));
@@ -917,12 +940,12 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     B->nnz = nnz;
 
     // outputs that exist even for an empty matrix
-    TRS_TRY(B->s_offset.alloc((size_t)W + 1));
-    TRS_TRY(B->s_window_tile_offset.alloc((size_t)W + 1));
-    TRS_TRY(B->t_row_offset.alloc(1));
-    TRS_TRY(B->t_block_offset.alloc(1));
-    TRS_TRY(B->c_row_offset.alloc(1));
-    TRS_TRY(B->cs_row_offset.alloc(1));
+    TRS_TRY(B->s_offset.alloc_from(B->arena, (size_t)W + 1));
+    TRS_TRY(B->s_window_tile_offset.alloc_from(B->arena, (size_t)W + 1));
+    TRS_TRY(B->t_row_offset.alloc_from(B->arena, 1));
+    TRS_TRY(B->t_block_offset.alloc_from(B->arena, 1));
+    TRS_TRY(B->c_row_offset.alloc_from(B->arena, 1));
+    TRS_TRY(B->cs_row_offset.alloc_from(B->arena, 1));
     TRS_CUDA(cudaMemsetAsync(B->s_offset.p, 0, sizeof(int) * (W + 1), st));
     TRS_CUDA(cudaMemsetAsync(B->s_window_tile_offset.p, 0, sizeof(int) * (W + 1), st));
     TRS_CUDA(cudaMemsetAsync(B->t_row_offset.p, 0, sizeof(int), st));
@@ -1124,11 +1147,11 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     // ---- 7. groups ---------------------------------------------------------------------------------
     int* grp_wcol;
     TRS_TRY(sc.get<int>((size_t)G * 4, &grp_wcol));
-    TRS_TRY(B->s_column.alloc((size_t)G * 4));
-    TRS_TRY(B->s_window.alloc(G));
-    TRS_TRY(B->s_mask.alloc((size_t)G * window));
-    TRS_TRY(B->s_value.alloc((size_t)G * window * 2));
-    TRS_TRY(B->s_pos.alloc((size_t)G * window * 2));
+    TRS_TRY(B->s_column.alloc_from(B->arena, (size_t)G * 4));
+    TRS_TRY(B->s_window.alloc_from(B->arena, G));
+    TRS_TRY(B->s_mask.alloc_from(B->arena, (size_t)G * window));
+    TRS_TRY(B->s_value.alloc_from(B->arena, (size_t)G * window * 2));
+    TRS_TRY(B->s_pos.alloc_from(B->arena, (size_t)G * window * 2));
     unsigned long long* d_dropped;
     TRS_TRY(sc.get<unsigned long long>(1, &d_dropped));
     TRS_CUDA(cudaMemsetAsync(d_dropped, 0, sizeof(unsigned long long), st));
@@ -1181,9 +1204,9 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     TRS_CUDA(cudaMemsetAsync(wc_slot, 0xFF, sizeof(int) * (size_t)D, st));
     TRS_CUDA(cudaMemsetAsync(blk_nnz + NB, 0, sizeof(int), st));
     B->t_block_offset.release();
-    TRS_TRY(B->t_block_offset.alloc((size_t)NB + 1));
-    TRS_TRY(B->t_column.alloc((size_t)NB * 8));
-    TRS_TRY(B->t_binary.alloc((size_t)NB * 2));
+    TRS_TRY(B->t_block_offset.alloc_from(B->arena, (size_t)NB + 1));
+    TRS_TRY(B->t_column.alloc_from(B->arena, (size_t)NB * 8));
+    TRS_TRY(B->t_binary.alloc_from(B->arena, (size_t)NB * 2));
     int tc_nnz = 0;
     if (NB > 0) {
         kb_tc_blocks<<<grid_for(NB), 256, 0, st>>>(blk_pos, blk_len, NB, ord, wc_col, wc_mask, B->t_column.p, B->t_binary.p,
@@ -1192,16 +1215,16 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     }
     TRS_TRY(cub_.exclusive_sum(blk_nnz, B->t_block_offset.p, (long long)NB + 1));
     TRS_TRY(read_int(B->t_block_offset.p + NB, st, &tc_nnz));
-    TRS_TRY(B->t_value.alloc(tc_nnz));
+    TRS_TRY(B->t_value.alloc_from(B->arena, tc_nnz));
     if (NB > 0) {
         kb_tc_values<<<grid_for(nnz), 256, 0, st>>>(keys, edge, wc_incl, nnz, wc_slot, B->t_binary.p, B->t_block_offset.p,
                                                      val, B->t_value.p);
         TRS_LAUNCH_CHECK();
     }
     B->t_row_offset.release();
-    TRS_TRY(B->t_row_offset.alloc((size_t)NP + 1));
-    TRS_TRY(B->t_window_row.alloc(NP));
-    TRS_TRY(B->t_atomic.alloc(NP));
+    TRS_TRY(B->t_row_offset.alloc_from(B->arena, (size_t)NP + 1));
+    TRS_TRY(B->t_window_row.alloc_from(B->arena, NP));
+    TRS_TRY(B->t_atomic.alloc_from(B->arena, NP));
     kb_tc_parts<<<grid_for(W), 256, 0, st>>>(wc_begin, b_idx, win_bb, part_off, win_cuda_unit, W, cfg.part_t,
                                               B->t_row_offset.p, B->t_window_row.p, B->t_atomic.p);
     TRS_LAUNCH_CHECK();
@@ -1222,16 +1245,16 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     }
     TRS_CUDA(cudaStreamSynchronize(st));
     B->c_row_offset.release(); B->cs_row_offset.release();
-    TRS_TRY(B->c_row_offset.alloc((size_t)tot[0] + 1));
-    TRS_TRY(B->c_row.alloc(tot[0]));
-    TRS_TRY(B->c_atomic.alloc(tot[0]));
-    TRS_TRY(B->c_column.alloc(tot[2]));
-    TRS_TRY(B->c_value.alloc(tot[2]));
-    TRS_TRY(B->cs_row_offset.alloc((size_t)tot[1] + 1));
-    TRS_TRY(B->cs_row.alloc(tot[1]));
-    TRS_TRY(B->cs_atomic.alloc(tot[1]));
-    TRS_TRY(B->cs_column.alloc(tot[3]));
-    TRS_TRY(B->cs_value.alloc(tot[3]));
+    TRS_TRY(B->c_row_offset.alloc_from(B->arena, (size_t)tot[0] + 1));
+    TRS_TRY(B->c_row.alloc_from(B->arena, tot[0]));
+    TRS_TRY(B->c_atomic.alloc_from(B->arena, tot[0]));
+    TRS_TRY(B->c_column.alloc_from(B->arena, tot[2]));
+    TRS_TRY(B->c_value.alloc_from(B->arena, tot[2]));
+    TRS_TRY(B->cs_row_offset.alloc_from(B->arena, (size_t)tot[1] + 1));
+    TRS_TRY(B->cs_row.alloc_from(B->arena, tot[1]));
+    TRS_TRY(B->cs_atomic.alloc_from(B->arena, tot[1]));
+    TRS_TRY(B->cs_column.alloc_from(B->arena, tot[3]));
+    TRS_TRY(B->cs_value.alloc_from(B->arena, tot[3]));
     kb_cuda_fill<<<grid_for(n), 256, 0, st>>>(n, window, cfg.part_c, cfg.short_size, win_cuda_unit, win_cb, wc_begin, s_idx,
                                                b_idx, cand, wc_col, wc_mask, wc_start, edge, val, off4, extra_off, extra_key,
                                                extra_at, B->c_row_offset.p,
@@ -1247,11 +1270,11 @@ int do_build(trs_builder* B, const int* rowptr, const int* col, const float* val
     TRS_TRY(cub_.exclusive_sum(win_T, B->s_window_tile_offset.p, W + 1));
     int T = 0;
     TRS_TRY(read_int(B->s_window_tile_offset.p + W, st, &T));
-    TRS_TRY(B->s_tile_window.alloc(T));
-    TRS_TRY(B->s_tile_group.alloc(T));
-    TRS_TRY(B->s_tile_column.alloc((size_t)T * 16));
-    TRS_TRY(B->s_packed_a.alloc((size_t)T * 64));
-    TRS_TRY(B->s_packed_meta.alloc((size_t)T * 8));
+    TRS_TRY(B->s_tile_window.alloc_from(B->arena, T));
+    TRS_TRY(B->s_tile_group.alloc_from(B->arena, T));
+    TRS_TRY(B->s_tile_column.alloc_from(B->arena, (size_t)T * 16));
+    TRS_TRY(B->s_packed_a.alloc_from(B->arena, (size_t)T * 64));
+    TRS_TRY(B->s_packed_meta.alloc_from(B->arena, (size_t)T * 8));
     if (T > 0) {
         kb_tiles<<<grid_for(T), 256, 0, st>>>(B->s_window_tile_offset.p, B->s_offset.p, W, T, B->s_tile_window.p,
                                                B->s_tile_group.p);
@@ -1300,15 +1323,22 @@ const void* array_ptr(const trs_builder* B, int id, size_t* elem) {
 
 }  // namespace
 
-extern "C" int trs_build_create(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
-                                const trs_build_config* cfg, void* stream, trs_builder** out) {
+static int build_impl(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
+                      const trs_build_config* cfg, void* arena, size_t arena_bytes, bool use_arena, void* stream,
+                      trs_builder** out) {
     if (!rowptr || !cfg || !out || n_rows <= 0) return TRS_E_ARG;
     *out = nullptr;
     if (cfg->window <= 0 || cfg->window > 16) return TRS_E_WINDOW;
     if (cfg->part_t <= 0 || cfg->part_c <= 0 || cfg->short_size < 0 || cfg->density < 0) return TRS_E_ARG;
+    if (use_arena && (!arena || ((uintptr_t)arena & 255))) return TRS_E_ARG;
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return TRS_E_NO_DEVICE;
     trs_builder* B = new trs_builder();
+    if (use_arena) {
+        B->arena_store.base = (unsigned char*)arena;
+        B->arena_store.cap = arena_bytes;
+        B->arena = &B->arena_store;
+    }
     B->cfg = BuildCfg{cfg->part_t, cfg->part_c, cfg->short_size, cfg->density, cfg->window, cfg->tc_min_util,
                       cfg->skip_tc, cfg->unit_min_nnz, cfg->strict ? 1 : 0};
     B->n_rows = n_rows;
@@ -1326,6 +1356,46 @@ extern "C" int trs_build_create(const int32_t* rowptr, const int32_t* col, const
     if (rc) { B->release(); delete B; return rc; }
     fill_sizes(B);
     *out = B;
+    return TRS_OK;
+}
+
+extern "C" int trs_build_create(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
+                                const trs_build_config* cfg, void* stream, trs_builder** out) {
+    return build_impl(rowptr, col, values, n_rows, cfg, nullptr, 0, false, stream, out);
+}
+
+// Upper bound of the device memory one build can need (outputs + temporaries), from the sizes
+// alone: every count the builder allocates by is bounded by the number of entries (distinct
+// (window, column) pairs <= nnz, units <= pairs / 2 + windows, groups <= pairs / 4 + windows, ...).
+extern "C" int trs_build_query(int n_rows, long long nnz, const trs_build_config* cfg, size_t* arena_bytes) {
+    if (!cfg || !arena_bytes || n_rows <= 0 || nnz < 0) return TRS_E_ARG;
+    if (cfg->window <= 0 || cfg->window > 16) return TRS_E_WINDOW;
+    const size_t W = (size_t)ceil_div(n_rows, cfg->window) + 1;
+    const size_t e = (size_t)nnz;
+    size_t b = 0;
+    b += e * 40;                      // row ids, two 64-bit key buffers, two edge buffers, heads, running counts
+    b += e * 72;                      // per-(window, column) records, their two sort buffers, TC / SPTC index maps
+    b += (e / 2 + W) * 8 + (e / 4 + W) * 24;   // units, pairs, group column lists
+    if (cfg->strict) b += e * 28 + (size_t)n_rows * 8;
+    b += W * 4 * 32;                  // per-window counters and prefixes
+    b += e / 2 + ((size_t)64 << 20);  // CUB temporary storage
+    // outputs: SPTC groups (196 B each) and tiles (360 B each), TC blocks, CSR parts, fp16 value copies
+    b += (e / 4 + W) * 196 + (e / 16 + 2 * W) * 360;
+    b += e * 12 + (e / 8 + W) * 64 + e * 14 + W * 32;
+    b += 256 * 160;                   // alignment of every block
+    *arena_bytes = b;
+    return TRS_OK;
+}
+
+extern "C" int trs_build_fill(const int32_t* rowptr, const int32_t* col, const float* values, int n_rows,
+                              const trs_build_config* cfg, void* arena, size_t arena_bytes, void* stream,
+                              trs_builder** out) {
+    return build_impl(rowptr, col, values, n_rows, cfg, arena, arena_bytes, true, stream, out);
+}
+
+extern "C" int trs_build_arena_used(const trs_builder* B, size_t* bytes) {
+    if (!B || !bytes) return TRS_E_ARG;
+    *bytes = B->arena ? B->arena->high : 0;
     return TRS_OK;
 }
 
@@ -1382,7 +1452,7 @@ extern "C" int trs_build_format(trs_builder* B, trs_format* out, void* stream) {
         {&B->t_value, &B->t_value_h}, {&B->c_value, &B->c_value_h}, {&B->cs_value, &B->cs_value_h}};
     for (auto& c : conv) {
         if (c.dst->p || c.src->n == 0) continue;
-        int rc = c.dst->alloc(c.src->n);
+        int rc = c.dst->alloc_from(B->arena, c.src->n);
         if (rc) return rc;
         kb_to_half<<<grid_for((long long)c.src->n), 256, 0, st>>>(c.src->p, (long long)c.src->n, c.dst->p);
         TRS_LAUNCH_CHECK();

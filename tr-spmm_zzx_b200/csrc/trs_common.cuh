@@ -25,19 +25,63 @@ namespace trs {
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline long long ceil_div64(long long a, long long b) { return (a + b - 1) / b; }
 
-// Simple owning device buffer for plan-lifetime index arrays.
+// Caller-owned device memory handed to a call that would otherwise allocate: blocks are cut off
+// the front (256-byte aligned); a block given back is kept on a free list and handed out again
+// to the next request it fits, which is what keeps the footprint of a pass with many temporaries
+// near its peak instead of its sum.  Not thread-safe: one arena serves one call at a time.
+struct Arena {
+    unsigned char* base = nullptr;
+    size_t cap = 0, used = 0, high = 0;
+    struct Free { unsigned char* p; size_t bytes; };
+    Free free_list[64];
+    int n_free = 0;
+    unsigned char* take(size_t bytes) {
+        bytes = (bytes + 255) & ~(size_t)255;
+        if (bytes == 0) bytes = 256;
+        int best = -1;
+        for (int i = 0; i < n_free; ++i)
+            if (free_list[i].bytes >= bytes && (best < 0 || free_list[i].bytes < free_list[best].bytes)) best = i;
+        if (best >= 0 && free_list[best].bytes <= bytes + bytes / 4) {   // close fit: reuse whole
+            unsigned char* p = free_list[best].p;
+            free_list[best] = free_list[--n_free];
+            return p;
+        }
+        if (used + bytes > cap) return nullptr;
+        unsigned char* p = base + used;
+        used += bytes;
+        if (used > high) high = used;
+        return p;
+    }
+    void give_back(void* p, size_t bytes) {
+        bytes = (bytes + 255) & ~(size_t)255;
+        if (bytes == 0) bytes = 256;
+        if ((unsigned char*)p + bytes == base + used) { used -= bytes; return; }   // last block: shrink
+        if (n_free < 64) free_list[n_free++] = Free{(unsigned char*)p, bytes};
+    }
+};
+
+// Simple owning device buffer for plan-lifetime index arrays; with an arena the memory is the
+// caller's and release() only forgets it.
 template <class T>
 struct DevBuf {
     T* p = nullptr;
     size_t n = 0;
-    int alloc(size_t count) {
+    bool owned = true;
+    int alloc(size_t count) { return alloc_from(nullptr, count); }
+    int alloc_from(Arena* arena, size_t count) {
         n = count;
         if (count == 0) { p = nullptr; return 0; }
+        if (arena) {
+            p = (T*)arena->take(count * sizeof(T));
+            owned = false;
+            return p ? 0 : TRS_E_WORKSPACE;
+        }
+        owned = true;
         cudaError_t e = cudaMalloc((void**)&p, count * sizeof(T));
         return e == cudaSuccess ? 0 : (int)e;
     }
     void release() {
-        if (p) cudaFree(p);
+        if (p && owned) cudaFree(p);
         p = nullptr;
         n = 0;
     }

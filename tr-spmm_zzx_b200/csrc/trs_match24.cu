@@ -4,6 +4,10 @@
 //   variant 0  matching_utils.match_2to4            TR-source/Block/block_matching_window_para_dr.cpp:90-261
 //   variant 1  matching_utils_hash.match_2to4_hash  TR-source/Block/block_matching_hash.cpp:104-283
 //   variant 2  matching_utils_bucket.match_2to4_bucket  TR-source/Block/block_matching_bucket.cpp:130-360
+//   variant 3  matching_utils_online.match_2to4_online  TR-source/Block/block_matching_online.cu:85-431
+//              (the dual-routing rules of variant 0 over the columns in the SLOT ORDER of the
+//              reference's 2048-entry open-addressing table, for the schedule in which the window's
+//              rows insert one after the other; at most 2048 distinct columns per window survive)
 //
 // All three are greedy first-fit scans over the window's columns (sorted by column id) and then
 // over the pairs they produced; every step depends on which columns earlier steps consumed, so a
@@ -31,6 +35,7 @@ struct MStats {  // device-side accumulators
     long long tc_total_nnz, tc_block_count;
     int tc_max_nnz, tc_min_nnz;
     long long fake_exact;  // 2 * win_rows * groups - nnz of the grouped columns (exact padding count)
+    long long pool_to_tc, pool_to_sptc;  // pooled columns routed to TC blocks / to 2-column fallback groups
 };
 
 struct WinCols {
@@ -107,14 +112,16 @@ __device__ __forceinline__ void flush_window(MStats* st, int groups, long long f
 // ---------------------------------------------------------------------------------------------
 // variant 0: sliding window + dense-pool dual routing
 // ---------------------------------------------------------------------------------------------
+// `fixed_rows` > 0: every padding count uses that many rows, whatever the window really holds
+// (block_matching_online.cu:332, 384 use the constant 32 = 2 x 16).
 __global__ void km_para_dr(WinCols wc, Work wk, int W, int n_rows, int window, int dense_threshold, int t_max,
-                           MStats* st) {
+                           int fixed_rows, MStats* st) {
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (w >= W) return;
     const int b = wc.begin[w], n = wc.begin[w + 1] - b;
     if (n == 0) return;
-    const int win_rows = min(window, n_rows - w * window);
+    const int win_rows = fixed_rows > 0 ? fixed_rows : min(window, n_rows - w * window);
     const unsigned short* m = wc.mask + b;
     unsigned short *G1 = wk.pG1 + b, *G2 = wk.pG2 + b;
     unsigned char *n1 = wk.pn1 + b, *n2 = wk.pn2 + b, *used = wk.pused + b, *pool = wk.pool + b;
@@ -175,6 +182,8 @@ __global__ void km_para_dr(WinCols wc, Work wk, int W, int n_rows, int window, i
         ++groups;
     }
     flush_window(st, groups, fake, fine, coarse);
+    atomicAdd((u64*)&st->pool_to_tc, (u64)processed);
+    atomicAdd((u64*)&st->pool_to_sptc, (u64)(nd - processed));
     if (tc_blocks) {
         atomicAdd((u64*)&st->tc_blocks, (u64)tc_blocks);
         atomicAdd((u64*)&st->tc_block_count, (u64)tc_blocks);
@@ -442,12 +451,70 @@ __global__ void km_heads(const u64* __restrict__ keys, long long nnz, int* __res
     if (i < nnz) head[i] = (i == 0 || (keys[i] >> 4) != (keys[i - 1] >> 4)) ? 1 : 0;
 }
 __global__ void km_records(const u64* __restrict__ keys, const int* __restrict__ head, const int* __restrict__ incl,
-                           long long nnz, int col_bits, unsigned* __restrict__ mask32, int* __restrict__ win_ncol) {
+                           long long nnz, int col_bits, unsigned* __restrict__ mask32, int* __restrict__ win_ncol,
+                           int* __restrict__ rec_col) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nnz) return;
     const int j = incl[i] - 1;
     atomicOr(&mask32[j], 1u << (unsigned)(keys[i] & 15));
-    if (head[i]) atomicAdd(&win_ncol[(int)(keys[i] >> (col_bits + 4))], 1);
+    if (head[i]) {
+        atomicAdd(&win_ncol[(int)(keys[i] >> (col_bits + 4))], 1);
+        if (rec_col) rec_col[j] = (int)((keys[i] >> 4) & ((1ull << col_bits) - 1ull));
+    }
+}
+
+// Variant 3 front end.  The reference inserts the window's entries into a 2048-slot table
+// (slot = col % 2048, linear probing, block_matching_online.cu:157-177) and compacts it in slot
+// order (:184-197).  For the schedule in which row 0 inserts all its entries, then row 1, ...,
+// a column is inserted when its first row is reached, in ascending column order inside that row:
+// insertion order = (lowest set bit of the row mask, column id).  One warp per window replays the
+// insertions in a shared-memory table (lane 0 probes; the 32 lanes find the next candidates with
+// ballots), stops when the table is full - later columns are lost, as in the reference - and
+// writes the surviving row masks in slot order.
+constexpr int kOnlineSlots = 2048;
+__global__ void __launch_bounds__(128) km_online_order(WinCols wc, const int* __restrict__ rec_col, int W,
+                                                       const int* __restrict__ out_begin,
+                                                       unsigned short* __restrict__ out_mask) {
+    __shared__ int table[4][kOnlineSlots];   // record index + 1, 0 = empty
+    const int wslot = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int w = blockIdx.x * 4 + wslot;
+    if (w >= W) return;
+    const int b = wc.begin[w], n = wc.begin[w + 1] - b;
+    if (n == 0) return;
+    int* tab = table[wslot];
+    for (int i = lane; i < kOnlineSlots; i += 32) tab[i] = 0;
+    __syncwarp();
+    int inserted = 0;
+    for (int r = 0; r < 16 && inserted < kOnlineSlots; ++r) {
+        for (int j0 = 0; j0 < n && inserted < kOnlineSlots; j0 += 32) {
+            const int j = j0 + lane;
+            const unsigned m = j < n ? wc.mask[b + j] : 0u;
+            unsigned bal = __ballot_sync(0xffffffffu, m != 0u && (__ffs(m) - 1) == r);
+            if (lane == 0) {
+                while (bal && inserted < kOnlineSlots) {
+                    const int jj = j0 + __ffs(bal) - 1;
+                    bal &= bal - 1;
+                    int slot = rec_col[b + jj] % kOnlineSlots;
+                    while (tab[slot] != 0) slot = (slot + 1) % kOnlineSlots;   // a free slot exists: inserted < slots
+                    tab[slot] = jj + 1;
+                    ++inserted;
+                }
+            }
+            inserted = __shfl_sync(0xffffffffu, inserted, 0);
+        }
+    }
+    __syncwarp();
+    int out = out_begin[w];
+    for (int s0 = 0; s0 < kOnlineSlots; s0 += 32) {
+        const int v = tab[s0 + lane];
+        const unsigned occ = __ballot_sync(0xffffffffu, v != 0);
+        if (v != 0) out_mask[out + __popc(occ & ((1u << lane) - 1u))] = wc.mask[b + v - 1];
+        out += __popc(occ);
+    }
+}
+__global__ void km_online_counts(const int* __restrict__ begin, int W, int* __restrict__ cnt) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w <= W) cnt[w] = w < W ? min(begin[w + 1] - begin[w], kOnlineSlots) : 0;
 }
 __global__ void km_narrow(const unsigned* __restrict__ mask32, int D, unsigned short* __restrict__ mask16) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -490,9 +557,10 @@ int bits_needed(long long max_value) { int b = 1; while ((1ll << b) <= max_value
 extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, int n_rows, int window,
                                  int dense_threshold, int t_max, void* stream, trs_match_stats* out) {
     if (!rowptr || !out || n_rows <= 0) return TRS_E_ARG;
-    if (variant < 0 || variant > 2) return TRS_E_ARG;
+    if (variant < 0 || variant > 3) return TRS_E_ARG;
     if (window <= 0 || window > 16) return TRS_E_WINDOW;
-    if (variant == 0 && (dense_threshold <= 0 || t_max < 0)) return TRS_E_ARG;
+    if ((variant == 0 || variant == 3) && (dense_threshold <= 0 || t_max < 0)) return TRS_E_ARG;
+    if (variant == 3 && window != 16) return TRS_E_WINDOW;   // the reference kernel fixes 16 rows per window
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return TRS_E_NO_DEVICE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -567,7 +635,9 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
     M_TRY(bag.get<int>((size_t)W + 1, &begin));
     TRS_CUDA(cudaMemsetAsync(mask32, 0, sizeof(unsigned) * (size_t)D, st));
     TRS_CUDA(cudaMemsetAsync(win_ncol, 0, sizeof(int) * ((size_t)W + 1), st));
-    km_records<<<gridm(nnz), 256, 0, st>>>(keys, head, incl, nnz, col_bits, mask32, win_ncol);
+    int* rec_col = nullptr;
+    if (variant == 3) M_TRY(bag.get<int>(D, &rec_col));
+    km_records<<<gridm(nnz), 256, 0, st>>>(keys, head, incl, nnz, col_bits, mask32, win_ncol, rec_col);
     km_narrow<<<gridm(D), 256, 0, st>>>(mask32, D, mask16);
     TRS_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, win_ncol, begin, W + 1, st));
     M_TRY(reserve(need));
@@ -594,7 +664,20 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
     WinCols wc{begin, mask16};
     const unsigned blocks = gridm((long long)W * 32, 128);
     if (variant == 0) {
-        km_para_dr<<<blocks, 128, 0, st>>>(wc, wk, W, n_rows, window, dense_threshold, t_max, d_stats);
+        km_para_dr<<<blocks, 128, 0, st>>>(wc, wk, W, n_rows, window, dense_threshold, t_max, 0, d_stats);
+    } else if (variant == 3) {
+        int *cnt2, *begin2;
+        unsigned short* mask2;
+        M_TRY(bag.get<int>((size_t)W + 1, &cnt2));
+        M_TRY(bag.get<int>((size_t)W + 1, &begin2));
+        M_TRY(bag.get<unsigned short>(D, &mask2));
+        km_online_counts<<<gridm(W + 1), 256, 0, st>>>(begin, W, cnt2);
+        TRS_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, cnt2, begin2, W + 1, st));
+        M_TRY(reserve(need));
+        TRS_CUDA(cub::DeviceScan::ExclusiveSum(tmp, need, cnt2, begin2, W + 1, st));
+        km_online_order<<<gridm(W, 4), 128, 0, st>>>(wc, rec_col, W, begin2, mask2);
+        WinCols wc2{begin2, mask2};
+        km_para_dr<<<blocks, 128, 0, st>>>(wc2, wk, W, n_rows, window, dense_threshold, t_max, 16, d_stats);
     } else if (variant == 1) {
         // columns of every window ordered by (mask, index): stable sort of (window, mask) keys
         u64 *mk_a, *mk_b;
@@ -629,5 +712,7 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
     out->tc_block_max_nnz = h.tc_max_nnz;
     out->tc_block_min_nnz = h.tc_min_nnz;
     out->fake_zeros_exact = h.fake_exact;
+    out->dense_to_tc_cols = h.pool_to_tc;
+    out->dense_to_sptc_cols = h.pool_to_sptc;
     return TRS_OK;
 }

@@ -9,6 +9,7 @@
 // with three shuffles.  The row of an entry is found once per warp by binary search in the row
 // pointers and then advanced linearly.
 #include <stdlib.h>
+#include <string.h>
 
 #include <cub/cub.cuh>
 
@@ -306,6 +307,118 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_pipe(const SddmmBlock* _
     }
 }
 
+// The same walk with both dependent loads of a block taken off the warp's critical path: the
+// 128-byte records run kRecAhead blocks ahead and the 8 gathered Y rows kRowAhead blocks ahead,
+// all as 16-byte cp.async copies into the warp's own rings in shared memory (one commit group per
+// block, lanes meet in one __syncwarp per block, no block-wide barrier).  A Y row lands with its
+// 16-byte chunks rotated by the row number (chunk c of row r at position c ^ r), which makes the
+// fragment reads - lane (g, t) takes chunks 4 ch + t of row g - conflict-free without padding.
+constexpr int kRecRing = 8, kRecAhead = 6, kRowAhead = 3, kRowStages = 4;
+
+template <int KCH>
+struct SddmmRing {
+    static constexpr int ROWB = KCH * 64;                 // bytes of a Y row (K halfs)
+    static constexpr int CPR = KCH * 4;                   // 16-byte chunks per row
+    static constexpr int STAGE = 8 * ROWB;
+    static constexpr int WARP_SMEM = kRecRing * 128 + kRowStages * STAGE;
+    static constexpr int SMEM = 4 * WARP_SMEM;
+};
+
+template <int KCH, int MINB>
+__global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* __restrict__ blk, long long n_blocks,
+                                                             const __half* __restrict__ X, const __half* __restrict__ Y,
+                                                             __half* __restrict__ out, int n_rows, int blocks_per_warp) {
+    using R = SddmmRing<KCH>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + wid;
+    const long long b0 = warp * blocks_per_warp;
+    if (b0 >= n_blocks) return;
+    const int nb = (int)(min(b0 + (long long)blocks_per_warp, n_blocks) - b0);
+    unsigned char* recs = smem + wid * R::WARP_SMEM;
+    unsigned char* rows = recs + kRecRing * 128;
+    const uint32_t recs0 = smem_u32(recs), rows0 = smem_u32(rows);
+    constexpr int ROW16 = KCH * 4;
+    const uint4* Xq = (const uint4*)X + t;
+    const uint4* Yq = (const uint4*)Y;
+
+    auto issue_rec = [&](int j) {   // record of block j -> record ring (8 lanes x 16 B)
+        if (j < nb && lane < 8) cp_async16(recs0 + (j & (kRecRing - 1)) * 128 + lane * 16, (const uint4*)(blk + b0 + j) + lane, 16);
+    };
+    // Y rows of block j (its record is in the ring): lane copies chunks (lane & 3) + 4 i of row lane >> 2
+    auto issue_rows = [&](int j) {
+        if (j >= nb) return;
+        const int c = *(const int*)(recs + (j & (kRecRing - 1)) * 128 + g * 4);
+        const uint4* src = Yq + (size_t)max(c, 0) * ROW16;
+        const uint32_t dst = rows0 + (j % kRowStages) * R::STAGE + g * R::ROWB;
+#pragma unroll
+        for (int i = 0; i < KCH; ++i) {
+            const int chunk = t + 4 * i;
+            cp_async16(dst + ((chunk ^ g) & (R::CPR - 1)) * 16, src + chunk, c >= 0 ? 16 : 0);
+        }
+    };
+    // group accounting: prologue = records 0 .. kRecAhead-1 (waited for), then one group per block j
+    // holding the rows of block j + kRowAhead and the record of block j + kRecAhead; the rows of
+    // blocks 0 .. kRowAhead-1 are kRowAhead groups of their own.  At iteration j all but the newest
+    // kRowAhead-1 groups are complete: the rows of block j and the record of block j + kRowAhead.
+#pragma unroll 1
+    for (int j = 0; j < kRecAhead; ++j) issue_rec(j);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < kRowAhead; ++j) {
+        issue_rows(j);
+        cp_async_commit();
+    }
+
+    int cur_w = -1;
+    uint4 xa[KCH], xb[KCH];
+#pragma unroll
+    for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < nb; ++j) {
+        cp_async_wait<kRowAhead - 1>();
+        __syncwarp();
+        issue_rec(j + kRecAhead);
+        issue_rows(j + kRowAhead);
+        cp_async_commit();
+        const unsigned char* rec = recs + (j & (kRecRing - 1)) * 128;
+        const int w = *(const int*)(rec + 48);
+        const unsigned wa = *(const unsigned*)(rec + 32 + (g >> 2) * 4), wb = *(const unsigned*)(rec + 32 + ((g >> 2) + 2) * 4);
+        if (w != cur_w) {  // warp-uniform
+            cur_w = w;
+            const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
+#pragma unroll
+            for (int ch = 0; ch < KCH; ++ch) {
+                xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
+                xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
+            }
+        }
+        const unsigned char* yrow = rows + (j % kRowStages) * R::STAGE + g * R::ROWB;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < KCH; ++ch) {
+            const uint4 y = *(const uint4*)(yrow + (((4 * ch + t) ^ g) & (R::CPR - 1)) * 16);
+            mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y.x, y.y);
+            mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y.z, y.w);
+        }
+        const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
+        const int n0 = 2 * t;
+        if ((ba >> n0) & 3u) {
+            const int s = *(const int*)(rec + 64 + g * 4) + __popc(ba & ((1u << n0) - 1u));
+            if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
+            if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
+        }
+        if ((bbits >> n0) & 3u) {
+            const int s = *(const int*)(rec + 64 + (g + 8) * 4) + __popc(bbits & ((1u << n0) - 1u));
+            if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
+            if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
+        }
+    }
+    cp_async_wait<0>();
+}
+
 }  // namespace trs
 
 struct trs_sddmm_plan {
@@ -449,7 +562,19 @@ extern "C" int trs_sddmm_plan_run(const trs_sddmm_plan* p, const trs_half* X, co
     const long long warps = trs::ceil_div64(p->n_blocks, bpw);
     const unsigned grid = (unsigned)trs::ceil_div64(warps, 4);
     const __half *x = (const __half*)X, *y = (const __half*)Y;
-    if (K == 32) trs::k_sddmm_tc_pipe<1, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+    static const bool ring = [] { const char* v = getenv("TRS_SDDMM_KERNEL"); return !(v && strcmp(v, "pipe") == 0); }();
+    if (ring) {
+        auto launch = [&](auto kernel, int smem) -> int {
+            TRS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            kernel<<<grid, 128, smem, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+            return TRS_OK;
+        };
+        int rc;
+        if (K == 32) rc = launch(trs::k_sddmm_tc_ring<1, 8>, trs::SddmmRing<1>::SMEM);
+        else if (K == 64) rc = launch(trs::k_sddmm_tc_ring<2, 8>, trs::SddmmRing<2>::SMEM);
+        else rc = launch(trs::k_sddmm_tc_ring<4, 5>, trs::SddmmRing<4>::SMEM);
+        if (rc) return rc;
+    } else if (K == 32) trs::k_sddmm_tc_pipe<1, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     else if (K == 64) trs::k_sddmm_tc_pipe<2, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     else trs::k_sddmm_tc_pipe<4, 5><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
     TRS_LAUNCH_CHECK();

@@ -275,40 +275,6 @@ __device__ __forceinline__ void finish_item(float (&acc)[4][4], const Item& it, 
     }
 }
 
-// Fused exchange epilogue (fp16 rows into several [N_total, F] buffers, e.g. the hidden matrix of a
-// GCN layer on every GPU of the box): the accumulators are converted once, staged as a 16 x FS
-// fp16 tile in shared memory, and each thread then writes 16-byte pieces of whole rows to every
-// destination — 256-byte contiguous row segments, which is what NVLink peer stores want.
-// `tile` must hold 16 * (FS * 2 + 16) bytes and be free (pipeline drained, block synchronised).
-template <int FS, int THREADS>
-__device__ __forceinline__ void finish_item_bcast(float (&acc)[4][4], const Item& it, const KernelArgs& a, int fbase,
-                                                  int wid, int g, int t, unsigned char* tile) {
-    constexpr int PITCH = FS * 2 + 16;
-    if (a.relu) {
-#pragma unroll
-        for (int n = 0; n < 4; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[n][i] = fmaxf(acc[n][i], 0.f);
-    }
-#pragma unroll
-    for (int n = 0; n < 4; ++n)
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-            *(__half2*)(tile + (g + 8 * h) * PITCH + (wid * 32 + n * 8 + 2 * t) * 2) =
-                __floats2half2_rn(acc[n][2 * h], acc[n][2 * h + 1]);
-    __syncthreads();
-    constexpr int CPR = FS / 8;
-    for (int c = threadIdx.x; c < 16 * CPR; c += THREADS) {
-        const int lr = c / CPR, ch = c % CPR;
-        const int f = fbase + ch * 8;
-        const long long row = (long long)it.window * a.window + lr;
-        if (lr >= a.window || row >= a.m_rows || f >= a.F) continue;
-        const uint4 v = *(const uint4*)(tile + lr * PITCH + ch * 16);
-        const size_t off = (size_t)(a.peer_row0 + row) * (size_t)a.F + f;
-        for (int d = 0; d < a.n_peers; ++d) *(uint4*)((__half*)a.peers[d] + off) = v;
-    }
-}
-
 template <int WARPS>
 struct Tile {
     static constexpr int FS = WARPS * 32;          // features per CTA
@@ -320,7 +286,7 @@ struct Tile {
     static constexpr int CPR = FS / 8;             // 16-byte chunks per B row
 };
 
-template <int WARPS, bool ALIGNED>
+template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) {
     using T = Tile<WARPS>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -358,31 +324,18 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
         }
     };
 
-    // each thread copies chunk (row0, ch) and (row0 + 8, ch) of every step when ALIGNED
-    const int ch = tid % T::CPR;
-    const int row0 = tid / T::CPR;  // 0..7
 
     auto issue = [&](int j) {  // j: step index relative to the item
         const int s = it.step_begin + j;
         unsigned char* st = smem + (j % kStages) * T::STAGE;
         const int* cols = idx_ring + (j % kIdxRing) * 16;
-        // ---- B rows
-        if (ALIGNED) {
-            const int c0 = cols[row0], c1 = cols[row0 + 8];
-            const int f = fbase + ch * 8;
-            const bool fin = f < a.F;  // F % 8 == 0 here, so a chunk is inside or outside
-            const __half* src0 = (c0 >= 0 && fin) ? a.B + (size_t)c0 * F + f : a.B;
-            const __half* src1 = (c1 >= 0 && fin) ? a.B + (size_t)c1 * F + f : a.B;
-            cp_async16(smem_u32(st + row0 * T::ROWB + ch * 16), src0, (c0 >= 0 && fin) ? 16 : 0);
-            cp_async16(smem_u32(st + (row0 + 8) * T::ROWB + ch * 16), src1, (c1 >= 0 && fin) ? 16 : 0);
-        } else {
-            for (int i = tid; i < 16 * T::FS; i += T::THREADS) {
-                const int r = i / T::FS, fo = i % T::FS;
-                const int c = cols[r];
-                __half v = __float2half(0.f);
-                if (c >= 0 && fbase + fo < a.F) v = a.B[(size_t)c * F + fbase + fo];
-                *(__half*)(st + r * T::ROWB + fo * 2) = v;
-            }
+        // ---- B rows: plain 2-byte loads (any alignment, any F)
+        for (int i = tid; i < 16 * T::FS; i += T::THREADS) {
+            const int r = i / T::FS, fo = i % T::FS;
+            const int c = cols[r];
+            __half v = __float2half(0.f);
+            if (c >= 0 && fbase + fo < a.F) v = a.B[(size_t)c * F + fbase + fo];
+            *(__half*)(st + r * T::ROWB + fo * 2) = v;
         }
         // ---- A operand
         unsigned char* as = st + T::BBYTES;
@@ -471,170 +424,6 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
     }
     cp_async_wait<0>();
 
-    finish_item(acc, it, a, fbase, wid, g, t);
-}
-
-// ----------------------------------------------------------------------------------------------
-// Lean variant of the cp.async kernel for the aligned case (F % 8 == 0, 16-byte aligned arrays).
-// Same pipeline and numerics as k_window_spmm<WARPS, true>; what changes is the instruction
-// count of the inner loop, which ncu showed to be the limiter (81 % issue-active, 131 warp
-// instructions per k-step):
-//   * stage and ring slots are compile-time constants (loop unrolled by the stage count),
-//   * source addresses are one 32-bit multiply-add (16-byte units) plus one wide add,
-//   * the dense TC operand comes pre-expanded from the plan through the same cp.async pipeline
-//     (no bitmap decoding in the loop),
-//   * all shared-memory addresses are hoisted out of the loop.
-// ----------------------------------------------------------------------------------------------
-// Shared memory of the lean kernel: the A operand of a step needs 512 bytes at most (two expanded
-// TC blocks; a packed tile with its metadata is 288).  With 4 stages that would leave room for 11
-// CTAs of 128 threads per SM, but holding the register allocation to the 40 registers this needs
-// (a launch bound of 11, or 12 with 3 stages) was measured slower on B200 (3.80 vs 3.3 ms at R-MAT
-// scale 21, 0.174 vs 0.158 ms on the clustered case): the kernel then re-computes addresses it
-// otherwise keeps in registers.  So no minimum is requested (a minimum of 1 would let the compiler
-// take 74 registers: 6 CTAs per SM, 3.81 ms): 48 registers, 10 CTAs per SM.
-template <int WARPS, int STAGES>
-struct LeanTile {
-    static constexpr int FS = WARPS * 32;
-    static constexpr int ROWB = FS * 2 + 16;
-    static constexpr int BBYTES = 16 * ROWB;
-    static constexpr int STAGE = BBYTES + 512;
-    static constexpr int RING = STAGES <= 4 ? 8 : 16;   // id ring slots: a power of two above 2 * STAGES - 2
-    static constexpr int SMEM = STAGE * STAGES + RING * 64;
-    static constexpr int THREADS = WARPS * 32;
-    static constexpr int CPR = FS / 8;
-};
-
-template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32) k_window_spmm_lean(const KernelArgs a) {
-    using T = LeanTile<WARPS, STAGES>;
-    constexpr int kStages = STAGES;                 // shadows the file-wide stage count
-    constexpr int kIdxAhead = 2 * STAGES - 2;       // column ids are fetched this many steps ahead (ring of T::RING)
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int wid = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int fbase = blockIdx.y * T::FS;
-
-    const Item it = a.items[blockIdx.x];
-    const int nsteps = it.step_end - it.step_begin;
-    const int nsparse = min(max(it.ntiles - it.step_begin, 0), nsteps);  // steps [0, nsparse) are packed tiles
-
-    const uint32_t smem0 = smem_u32(smem);
-    const uint32_t ring0 = smem0 + T::STAGE * kStages;
-    const int* ring = (const int*)(smem + T::STAGE * kStages);
-
-    const int ch = tid % T::CPR, row0 = tid / T::CPR;
-    const uint32_t pitch16 = (uint32_t)a.F >> 3;             // 16-byte units per B row
-    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;    // this thread's chunk inside a row
-    const bool fin = fbase + ch * 8 < a.F;
-    const uint4* Bq = (const uint4*)a.B;
-    const uint32_t dst0 = smem0 + row0 * T::ROWB + ch * 16;
-    const int mtx = lane >> 3;
-    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + (wid * 32 + (mtx >> 1) * 8) * 2;
-    const unsigned char* a_lane = smem + T::BBYTES;          // + stage * STAGE
-
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-    auto issue_idx = [&](int m) {
-        if (tid < 4 && m < nsteps) {
-            const int s = it.step_begin + m;
-            const uint32_t dst = ring0 + (m & (T::RING - 1)) * 64 + tid * 16;
-            if (s < it.ntiles) {
-                cp_async16(dst, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + tid * 4, 16);
-            } else {
-                const int b = it.blk0 + 2 * (s - it.ntiles) + (tid >> 1);
-                if (b < it.blk_end) cp_async16(dst, a.f.t_column + (size_t)b * 8 + (tid & 1) * 4, 16);
-                else *(int4*)(smem + T::STAGE * kStages + (m & (T::RING - 1)) * 64 + tid * 16) = make_int4(-1, -1, -1, -1);
-            }
-        }
-    };
-
-    auto issue = [&](int j, int stage) {
-        const int* cols = ring + (j & (T::RING - 1)) * 16;
-        const int c0 = cols[row0], c1 = cols[row0 + 8];
-        const uint32_t o0 = (uint32_t)max(c0, 0) * pitch16 + chunk16;
-        const uint32_t o1 = (uint32_t)max(c1, 0) * pitch16 + chunk16;
-        cp_async16(dst0 + stage * T::STAGE, Bq + o0, (c0 >= 0 && fin) ? 16 : 0);
-        cp_async16(dst0 + stage * T::STAGE + 8 * T::ROWB, Bq + o1, (c1 >= 0 && fin) ? 16 : 0);
-        if (tid < 32) {  // A operand: warp 0
-            const int s = it.step_begin + j;
-            const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + tid * 16;
-            if (s < it.ntiles) {
-                const size_t tile = (size_t)(it.tile0 + s);
-                if (tid < 16) cp_async16(adst, a.f.s_packed_a + tile * 64 + tid * 4, 16);
-                else if (tid < 18) cp_async16(adst, a.f.s_packed_meta + tile * 8 + (tid - 16) * 4, 16);
-            } else {
-                const int b = it.blk0 + 2 * (s - it.ntiles) + (tid >> 4);
-                const bool live = b < it.blk_end;
-                cp_async16(adst, a.tc_dense + (size_t)(live ? b : it.blk0) * 128 + (tid & 15) * 8, live ? 16 : 0);
-            }
-        }
-    };
-
-    auto compute = [&](int j, int stage) {
-        const unsigned char* as = a_lane + stage * T::STAGE;
-        const uint32_t baddr = boff + stage * T::STAGE;
-        if (j < nsparse) {
-            const uint2 av = *(const uint2*)(as + lane * 8);
-            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
-                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
-            }
-        } else {
-            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
-            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
-            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
-            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
-                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
-            }
-        }
-    };
-
-#pragma unroll
-    for (int m = 0; m < kIdxAhead; ++m) issue_idx(m);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < kStages - 1; ++j) {
-        if (j < nsteps) issue(j, j);
-        cp_async_commit();
-    }
-    for (int j0 = 0; j0 < nsteps; j0 += kStages) {
-#pragma unroll
-        for (int u = 0; u < kStages; ++u) {
-            const int j = j0 + u;
-            if (j < nsteps) {
-                cp_async_wait<kStages - 2>();
-                __syncthreads();
-                issue_idx(j + kIdxAhead);
-                if (j + kStages - 1 < nsteps) issue(j + kStages - 1, (u + kStages - 1) % kStages);
-                cp_async_commit();
-                compute(j, u);
-            }
-        }
-    }
-    cp_async_wait<0>();
-    if (a.n_peers > 0 && it.slot < 0) {
-        __syncthreads();  // every warp is done with the pipeline buffers
-        add_csr_parts(acc, it, a, fbase, wid, g, t);
-        finish_item_bcast<T::FS, T::THREADS>(acc, it, a, fbase, wid, g, t, smem);
-        return;
-    }
     finish_item(acc, it, a, fbase, wid, g, t);
 }
 
@@ -1266,28 +1055,12 @@ static int launch_warp_kernel(const KernelArgs& a, cudaStream_t st) {
     return TRS_OK;
 }
 
-template <int FS, int MINB>
-static int launch_warp_stages(const KernelArgs& a, cudaStream_t st) {
-    static const int stages = env_int("TRS_WARP_STAGES", 3);
-    if (stages == 3) return launch_warp_kernel<FS, 3, MINB>(a, st);
-    if (stages == 4) return launch_warp_kernel<FS, 4, MINB>(a, st);
-    return launch_warp_kernel<FS, 2, MINB>(a, st);
-}
-
 template <int WARPS>
-static int launch_cta_kernel(const KernelArgs& a, bool lean, cudaStream_t st) {
+static int launch_cta_kernel(const KernelArgs& a, cudaStream_t st) {
     using T = Tile<WARPS>;
     dim3 grid(a.n_items, ceil_div(a.F, T::FS));
-    if (lean) {
-        using L = LeanTile<WARPS, 3>;
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM));
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm_lean<WARPS, 3>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared));
-        k_window_spmm_lean<WARPS, 3><<<grid, L::THREADS, L::SMEM, st>>>(a);
-    } else {
-        TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
-        k_window_spmm<WARPS, false><<<grid, T::THREADS, T::SMEM, st>>>(a);
-    }
+    TRS_CUDA(cudaFuncSetAttribute(k_window_spmm<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+    k_window_spmm<WARPS><<<grid, T::THREADS, T::SMEM, st>>>(a);
     TRS_LAUNCH_CHECK();
     return TRS_OK;
 }
@@ -1351,24 +1124,18 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     // The warp-owner kernel moves everything in 16-byte pieces; anything else takes the fallback.
     const bool aligned = p->arrays_aligned && (F % 8 == 0) &&
                          ((((uintptr_t)B | (uintptr_t)C | (uintptr_t)workspace) & 15) == 0);
-    static const int kernel_sel = [] {
-        const char* v = getenv("TRS_SPMM_KERNEL");
-        return !v ? 0 : strcmp(v, "lean") == 0 ? 1 : strcmp(v, "fallback") == 0 ? 2 : 0;
-    }();
-    static const int warp_fs = env_int("TRS_WARP_FS", 128);
+    // Three stages (two k-steps in flight per warp) measured fastest at R-MAT scale 21: 3.64 / 3.03 /
+    // 3.18 ms for 2 / 3 / 4 stages (more stages leave fewer warps per SM: shared memory is the limit);
+    // 64-feature slabs for F = 128 (24 warps per SM, twice the steps) were slower too (3.46 ms).
     int rc;
-    if (!aligned || (kernel_sel == 2 && n_peers == 0)) {
+    if (!aligned) {
         if (n_peers > 0) return TRS_E_ARG;
-        if (F <= 32) rc = launch_cta_kernel<1>(a, false, st);
-        else if (F <= 64) rc = launch_cta_kernel<2>(a, false, st);
-        else rc = launch_cta_kernel<4>(a, false, st);
-    } else if (kernel_sel == 1 && n_peers == 0) {
-        if (F <= 32) rc = launch_cta_kernel<1>(a, true, st);
-        else if (F <= 64) rc = launch_cta_kernel<2>(a, true, st);
-        else rc = launch_cta_kernel<4>(a, true, st);
-    } else if (F <= 32) rc = launch_warp_stages<32, 32>(a, st);
-    else if (F <= 64 || warp_fs == 64) rc = launch_warp_stages<64, 24>(a, st);
-    else rc = launch_warp_stages<128, 16>(a, st);   // F > 128: feature slabs of 128 on gridDim.y
+        if (F <= 32) rc = launch_cta_kernel<1>(a, st);
+        else if (F <= 64) rc = launch_cta_kernel<2>(a, st);
+        else rc = launch_cta_kernel<4>(a, st);
+    } else if (F <= 32) rc = launch_warp_kernel<32, 3, 32>(a, st);
+    else if (F <= 64) rc = launch_warp_kernel<64, 3, 24>(a, st);
+    else rc = launch_warp_kernel<128, 3, 16>(a, st);   // F > 128: feature slabs of 128 on gridDim.y
     if (rc) return rc;
     if (n_heavy > 0) {
         PeerDst pd;

@@ -108,6 +108,12 @@ def load():
     for name in ("trs_sddmm_plan_create", "trs_sddmm_plan_run", "trs_sddmm_plan_info", "trs_sddmm_plan_destroy"):
         getattr(lib, name).restype = i32
     lib.trs_build_create.argtypes = [vp, vp, vp, i32, C.POINTER(TrsBuildConfig), vp, C.POINTER(vp)]
+    lib.trs_build_fill.argtypes = [vp, vp, vp, i32, C.POINTER(TrsBuildConfig), vp, sz, vp, C.POINTER(vp)]
+    lib.trs_build_fill.restype = i32
+    lib.trs_build_query.argtypes = [i32, C.c_longlong, C.POINTER(TrsBuildConfig), C.POINTER(sz)]
+    lib.trs_build_query.restype = i32
+    lib.trs_build_arena_used.argtypes = [vp, C.POINTER(sz)]
+    lib.trs_build_arena_used.restype = i32
     lib.trs_build_destroy.argtypes = [vp]
     lib.trs_build_sizes.argtypes = [vp, C.POINTER(C.c_longlong)]
     lib.trs_build_stats.argtypes = [vp, C.POINTER(TrsBuildStats)]

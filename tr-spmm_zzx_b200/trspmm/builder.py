@@ -46,13 +46,25 @@ def env_switches():
     return skip_tc, unit_min
 
 
+def arena_bytes(n_rows: int, nnz: int, window: int = 16, strict: bool = False) -> int:
+    """trs_build_query: upper bound of the device memory one build of a matrix of this size needs."""
+    cfg = _lib.TrsBuildConfig(32, 32, 3, 8, window, 0.0, 0, 2, int(bool(strict)))
+    n = C.c_size_t()
+    _lib.check(_lib.load().trs_build_query(int(n_rows), int(nnz), C.byref(cfg), C.byref(n)))
+    return n.value
+
+
 def build_format(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, part_t: int = 32, part_c: int = 32,
                  short_size: int = 3, density: int = 8, window: int = 16, tc_min_util: float = 0.0,
-                 skip_tc: bool | None = None, unit_min_nnz: int | None = None, strict: bool = False):
+                 skip_tc: bool | None = None, unit_min_nnz: int | None = None, strict: bool = False,
+                 arena: torch.Tensor | None = None):
     """Build on the GPU.  Inputs: CUDA int32 row pointers / columns (canonical CSR) and fp32 values.
     Returns (Format on the same device, stats dict).  strict=True builds a lossless format: the
     entries the reference drops (third / fourth non-zero of a row inside a 4-column group) go to the
-    row's CUDA-core part; those arrays are then no longer bit-identical to the reference's."""
+    row's CUDA-core part; those arrays are then no longer bit-identical to the reference's.
+    With `arena` (a uint8 CUDA tensor, see arena_bytes) the library allocates nothing
+    (trs_build_fill): outputs and temporaries are cut out of the arena and the returned arrays are
+    views of it, valid until the caller reuses that memory; stats["arena_used"] is the high-water mark."""
     dev = rowptr.device
     if dev.type != "cuda":
         raise ValueError("build_format needs CUDA tensors (there is no CPU fallback)")
@@ -67,11 +79,22 @@ def build_format(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, par
                               int(e_min if unit_min_nnz is None else unit_min_nnz), int(bool(strict)))
     lib = _lib.load()
     handle = C.c_void_p()
+    if arena is not None:
+        if arena.device != dev or arena.dtype != torch.uint8 or not arena.is_contiguous():
+            raise ValueError("arena must be a contiguous uint8 tensor on the inputs' device")
+        base = arena.data_ptr()
+        skip = (-base) % 256                      # the library wants a 256-byte aligned start
+        if arena.numel() <= skip:
+            raise ValueError("arena too small")
+    arena_used = 0
     with torch.cuda.device(dev):
         stream = _lib.current_stream_ptr(dev)
-        _lib.check(lib.trs_build_create(rowptr.data_ptr(), col.data_ptr() if col.numel() else None,
-                                        val.data_ptr() if val.numel() else None, rowptr.numel() - 1,
-                                        C.byref(cfg), stream, C.byref(handle)))
+        args = (rowptr.data_ptr(), col.data_ptr() if col.numel() else None, val.data_ptr() if val.numel() else None,
+                rowptr.numel() - 1, C.byref(cfg))
+        if arena is None:
+            _lib.check(lib.trs_build_create(*args, stream, C.byref(handle)))
+        else:
+            _lib.check(lib.trs_build_fill(*args, base + skip, arena.numel() - skip, stream, C.byref(handle)))
         try:
             sizes = (C.c_longlong * len(FORMAT_NAMES))()
             _lib.check(lib.trs_build_sizes(handle, sizes))
@@ -79,14 +102,27 @@ def build_format(rowptr: torch.Tensor, col: torch.Tensor, val: torch.Tensor, par
             _lib.check(lib.trs_build_stats(handle, C.byref(stats)))
             arrays = []
             for i, name in enumerate(FORMAT_NAMES):
-                t = torch.empty(int(sizes[i]), dtype=_DTYPES.get(name, torch.int32), device=dev)
-                if t.numel():
-                    _lib.check(lib.trs_build_copy(handle, i, t.data_ptr(), 0, stream))
-                arrays.append(t.view(_shape(name, int(sizes[i]), window)))
+                dt = _DTYPES.get(name, torch.int32)
+                n_el = int(sizes[i])
+                if arena is None:
+                    t = torch.empty(n_el, dtype=dt, device=dev)
+                    if n_el:
+                        _lib.check(lib.trs_build_copy(handle, i, t.data_ptr(), 0, stream))
+                elif n_el:
+                    off = int(lib.trs_build_array(handle, i)) - base
+                    t = arena[off:off + n_el * torch.empty(0, dtype=dt).element_size()].view(dt)
+                else:
+                    t = torch.empty(0, dtype=dt, device=dev)
+                arrays.append(t.view(_shape(name, n_el, window)))
+            if arena is not None:
+                used = C.c_size_t()
+                _lib.check(lib.trs_build_arena_used(handle, C.byref(used)))
+                arena_used = used.value + skip
             torch.cuda.current_stream(dev).synchronize()
         finally:
             lib.trs_build_destroy(handle)
     info = {n: getattr(stats, n) for n, _ in stats._fields_}
+    info["arena_used"] = arena_used
     return Format(arrays, window), info
 
 

@@ -18,18 +18,21 @@ from .spmm import SpmmPlan
 
 
 class ShardedGCN2:
-    def __init__(self, rowptr, col, val, rank: int = 0, world: int = 1, window: int = 16, cuts=None, group=None):
+    def __init__(self, rowptr, col, val, rank: int = 0, world: int = 1, window: int = 16, cuts=None, group=None,
+                 strict: bool = False):
         self.n = rowptr.numel() - 1
         self.rank, self.world, self.group = rank, world, group
         self.cuts = cuts if cuts is not None else shard.balanced_window_cuts(rowptr, world, window)
         self.r0, self.r1 = self.cuts[rank], self.cuts[rank + 1]
         rp_l, col_l, val_l = shard.slice_csr(rowptr, col, val, self.r0, self.r1)
-        self.fmt, self.stats = build_format(rp_l, col_l, val_l, window=window)
+        self.fmt, self.stats = build_format(rp_l, col_l, val_l, window=window, strict=strict)
         self.plan = SpmmPlan(self.fmt, max(self.r1 - self.r0, 1), self.n, window)
         self.gather_bytes = 0
         self.profile = False
         self.last_breakdown = {}
         self._symm = {}   # feature width -> (tensor, handle) of the peer-mapped hidden matrix
+        self._copy_streams = None
+        self.push_chunks = 2
 
     def _symmetric(self, F: int, device):
         """A [N, F] fp16 matrix every rank of the box can store into (torch symmetric memory)."""
@@ -69,7 +72,9 @@ class ShardedGCN2:
         the output, [r1 - r0, F2] fp16.  gather="h1" exchanges the hidden matrix (N x F1) with NCCL;
         gather="z2" multiplies the own rows by W2 first and exchanges N x F2 instead;
         gather="fused" lets the layer-1 SpMM store its rows into every rank's H1 itself
-        (peer-mapped symmetric memory, trs_spmm_run_bcast)."""
+        (peer-mapped symmetric memory, trs_spmm_run_bcast); gather="push" multiplies the own rows by W2 in
+        window chunks and has the copy engines push each finished chunk into the peers' Z2 while the
+        next chunk is computed."""
         self.gather_bytes = 0
         r0, r1 = self.r0, self.r1
         marks = []
@@ -116,8 +121,54 @@ class ShardedGCN2:
             mark("spmm1+gemm2")
             self._exchange(z2)
             mark("exchange")
+        elif gather == "push":
+            # own rows -> ReLU -> x W2 in window chunks; every finished chunk is pushed into the peers'
+            # copies of Z2 by the copy engines (peer-mapped symmetric memory) while the next chunk is
+            # still being multiplied; exact row counts, no padding, no collective kernel on the SMs
+            if self.world == 1:
+                h1_local = self.plan.run(z1, relu=True)
+                z2 = torch.matmul(h1_local[: r1 - r0], W2)
+                mark("spmm1+gemm2")
+            else:
+                z2, hdl = self._symmetric(W2.shape[1], X.device)
+                if self._copy_streams is None:
+                    self._copy_streams = [torch.cuda.Stream(X.device) for _ in range(min(4, self.world - 1))]
+                key = ("peers", W2.shape[1])
+                if key not in self._symm:
+                    self._symm[key] = [hdl.get_buffer(p, (self.n, W2.shape[1]), torch.float16) for p in range(self.world)]
+                peers = self._symm[key]
+                hdl.barrier(channel=0)                 # every rank is done reading the previous Z2
+                main = torch.cuda.current_stream(X.device)
+                if r1 > r0:
+                    h1_local = torch.empty((r1 - r0, W1.shape[1]), dtype=torch.float16, device=X.device)
+                    W = self.plan.num_windows
+                    nch = max(1, min(self.push_chunks, W))
+                    k = 0
+                    for i in range(nch):
+                        w0, w1 = W * i // nch, W * (i + 1) // nch
+                        a0, a1 = w0 * self.plan.window, min(w1 * self.plan.window, r1 - r0)
+                        if a1 <= a0:
+                            continue
+                        self.plan.run_windows(z1, h1_local, w0, w1, relu=True)
+                        torch.matmul(h1_local[a0:a1], W2, out=z2[r0 + a0:r0 + a1])
+                        ready = torch.cuda.Event()
+                        ready.record(main)
+                        for p in range(self.world):
+                            if p == self.rank:
+                                continue
+                            cs = self._copy_streams[k % len(self._copy_streams)]
+                            k += 1
+                            cs.wait_event(ready)
+                            with torch.cuda.stream(cs):
+                                peers[p][r0 + a0:r0 + a1].copy_(z2[r0 + a0:r0 + a1], non_blocking=True)
+                        self.gather_bytes += (self.world - 1) * (a1 - a0) * W2.shape[1] * 2
+                    for cs in self._copy_streams:
+                        main.wait_stream(cs)
+                mark("spmm1+gemm2+push")
+                hdl.barrier(channel=1)                 # all rows of all ranks have landed
+                mark("barrier")
         else:
-            raise ValueError("gather must be 'h1', 'z2' or 'fused'")
+            raise ValueError("gather must be 'h1', 'z2', 'fused' or 'push'")
         out = self.plan.run(z2)[: r1 - r0] if r1 > r0 else z2[:0]
         mark("spmm2")
         if self.profile:

@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 
-VARIANTS = {"para_dr": 0, "hash": 1, "bucket": 2}
+VARIANTS = {"para_dr": 0, "hash": 1, "bucket": 2, "online": 3}
 
 
 class TrsMatchStats(C.Structure):
@@ -20,7 +20,8 @@ class TrsMatchStats(C.Structure):
                 ("block_padding_groups", C.c_longlong), ("fine_fallback", C.c_longlong),
                 ("coarse_fallback", C.c_longlong), ("fake_zeros", C.c_longlong), ("tc_total_nnz", C.c_longlong),
                 ("tc_block_count", C.c_longlong), ("tc_block_max_nnz", C.c_int32), ("tc_block_min_nnz", C.c_int32),
-                ("fake_zeros_exact", C.c_longlong)]
+                ("fake_zeros_exact", C.c_longlong), ("dense_to_tc_cols", C.c_longlong),
+                ("dense_to_sptc_cols", C.c_longlong)]
 
 
 def _as_int32(x: int) -> int:
