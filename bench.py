@@ -167,6 +167,45 @@ def dropped_rows(fmt):
     return torch.unique(fmt.s_window[g].long() * 16 + r)
 
 
+def kept_entry_mask(rp_l, col_l, fmt, n_cols):
+    """1 for every CSR entry of this rank's rows that the built format still holds, 0 for the
+    entries the reference builder's 2-per-group rule dropped (block_online.cpp:683-695): a bit of
+    a group's row mask whose position is in neither of the row's two slots."""
+    dev = col_l.device
+    keep = torch.ones(col_l.numel(), dtype=torch.uint8, device=dev)
+    if fmt.s_mask.numel() == 0:
+        return keep
+    G = fmt.s_mask.numel() // 16
+    m = fmt.s_mask.reshape(G, 16).to(torch.int32)
+    pos = fmt.s_pos.reshape(G, 16, -1).to(torch.int32)
+    cols4 = fmt.s_column.reshape(G, 4).long()
+    win = fmt.s_window.reshape(G).long()
+    rows_l, cols_l = [], []
+    for c in range(4):
+        lost = (((m >> c) & 1) == 1) & ~(pos == c).any(-1)
+        g, r = torch.nonzero(lost, as_tuple=True)
+        rows_l.append(win[g] * 16 + r)
+        cols_l.append(cols4[g, c])
+    rows_d, cols_d = torch.cat(rows_l), torch.cat(cols_l)
+    if rows_d.numel() == 0:
+        return keep
+    cnt = (rp_l[1:] - rp_l[:-1]).long()
+    row_of = torch.repeat_interleave(torch.arange(cnt.numel(), device=dev), cnt)
+    keys = row_of * n_cols + col_l.long()              # ascending: canonical CSR
+    idx = torch.searchsorted(keys, rows_d * n_cols + cols_d)
+    idx = idx.clamp_max(keys.numel() - 1)
+    hit = keys[idx] == rows_d * n_cols + cols_d
+    keep[idx[hit]] = 0
+    return keep
+
+
+def rel_error(got, ref):
+    """|x - y| / max(|y|, 1e-3 * largest |y| of the row): (max, mean) over all elements."""
+    scale = torch.maximum(ref.abs(), 1e-3 * ref.abs().amax(dim=1, keepdim=True)).clamp_min(1e-30)
+    rel = (got - ref).abs() / scale
+    return float(rel.max()), float(rel.mean())
+
+
 def parity_sample(rp_l, col_l, val_l, fmt, B, out, n_sample=4096, seed=123):
     """Checker run after the timed region, on every rank: `n_sample` of this rank's own rows that
     lost no entry, recomputed as a CSR product in fp32 by torch.sparse on the GPU (fp16-rounded
@@ -374,7 +413,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.empty_cache()
 
     # ---- e2e with HOST buffers: B from pinned host memory, C back to the host, every step
-    e2e_steps = max(2, min(args.steps, 8))
+    e2e_steps = max(2, min(args.steps, 20))
     h2d = d2h = 0.0
     legs = {k: 0.0 for k in LEG_NAMES}
     if world == 1:
@@ -731,7 +770,7 @@ def run_gcn(args, rank, world, local_rank):
     X = torch.randn(n, 256, device=dev, generator=g).half()
     W1 = (torch.randn(256, 128, device=dev, generator=g) * 0.02).half()
     W2 = (torch.randn(128, 64, device=dev, generator=g) * 0.02).half()
-    model = ShardedGCN2(rp, col, val, rank, world)
+    model = ShardedGCN2(rp, col, val, rank, world, strict=args.strict)
     kept = model.stats["nnz"] - model.stats["dropped_nnz"]
     for _ in range(args.warmup):
         model.forward(X, W1, W2, gather=args.gather)
@@ -753,6 +792,37 @@ def run_gcn(args, rank, world, local_rank):
     model.profile = True
     model.forward(X, W1, W2, gather=args.gather)
     breakdown = {k: round(v, 3) for k, v in model.last_breakdown.items()}
+    # checker, after the timed region, on every rank: the whole two-layer forward recomputed with
+    # torch.sparse (fp32 products, fp16 at the same stage boundaries) over the entries the built
+    # format holds, compared on this rank's own rows
+    model.profile = False
+    out = model.forward(X, W1, W2, gather=args.gather)
+    r0, r1 = model.r0, model.r1
+    keep = torch.ones(nnz, dtype=torch.uint8, device=dev)
+    if r1 > r0 and not args.strict:     # the lossless format keeps every entry
+        e_lo, e_hi = int(rp[r0]), int(rp[r1])
+        rp_l = (rp[r0:r1 + 1] - rp[r0]).contiguous()
+        keep[e_lo:e_hi] = kept_entry_mask(rp_l, col[e_lo:e_hi], model.fmt, n)
+    if world > 1:
+        dist.all_reduce(keep, op=dist.ReduceOp.MIN)
+    A = torch.sparse_csr_tensor(rp.long(), col.long(), val.half().float() * keep.float(), (n, n))
+    h1_ref = torch.relu(torch.sparse.mm(A, torch.matmul(X, W1).float())).half()
+    ref = torch.sparse.mm(A, torch.matmul(h1_ref, W2).float())[r0:r1]
+    # two fp16 roundings sit between the input and the output, and W2 has both signs: an output far
+    # below its row's largest magnitude carries the rounding noise of larger terms, so the largest
+    # error is taken against the row's largest |reference| and the mean against the element itself
+    if r1 > r0:
+        p_mean = rel_error(out.float(), ref)[1]
+        p_max = float(((out.float() - ref).abs() / ref.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)).max())
+    else:
+        p_max = p_mean = 0.0
+    del A, ref, h1_ref
+    pt = torch.tensor([p_max, p_mean], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    p_max, p_mean = float(pt[0]), float(pt[1])
+    if p_max > 4e-3 or p_mean > 1e-3:
+        raise RuntimeError(f"parity check failed: max row-normalised error {p_max}, mean rel {p_mean} (bars 4e-3 / 1e-3)")
     if rank == 0:
         ms, kept_total = float(t[0]), float(t[1])
         flops = 2.0 * kept_total * (128 + 64) + 2.0 * n * (256 * 128 + 128 * 64)
@@ -762,8 +832,13 @@ def run_gcn(args, rank, world, local_rank):
                           "dtype": "f16 in / f32 accumulate", "data": "synthetic",
                           "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather,
                                      "n_rows": n, "nnz": nnz, "kept_nnz": int(kept_total),
+                                     "format": "lossless (strict)" if args.strict else "reference-compatible (drops reproduced)",
                                      "gather_bytes_received_rank0": model.gather_bytes,
-                                     "stage_ms_rank0": breakdown}}), flush=True)
+                                     "stage_ms_rank0": breakdown},
+                          "parity_sample": {"max_row_normalised": p_max, "mean_rel": p_mean, "rows": n, "bars": [4e-3, 1e-3],
+                                            "checker": "torch.sparse CSR fp32 two-layer forward over the entries the built "
+                                                       "format holds, fp16 at the stage boundaries, every rank's own rows, "
+                                                       "worst rank reported"}}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -267,6 +267,11 @@ int trs_debug_stdsort_order(const unsigned char* keys, int n, int* out, int* hea
  *              open-addressing table filled by racing threads; this is its result for the
  *              schedule in which the rows of a window insert one after the other (window = 16,
  *              columns beyond the 2048th distinct one of a window are lost, as in the reference)
+ *   variant 4  matching_utils_cuda.match_2to4 (block_match_cuda.cu:822-1201, 1216-1612): the rules
+ *              of the reference's multi-block kernels (hash-table compaction order, overlap <= 12,
+ *              best score, search windows by window size) for the schedule in which its warps run
+ *              one at a time and the window's entries are inserted in ascending column order;
+ *              rows with ascending column ids are assumed.
  * dense_threshold / t_max are used by variants 0 and 3 only (the others fix their thresholds). */
 typedef struct trs_match_stats {
     int32_t total_rows, total_cols;

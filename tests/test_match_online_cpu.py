@@ -1,5 +1,6 @@
-"""CPU checks of the plain-Python replay of the reference's online matcher
-(Block/block_matching_online.cu:85-431), on cases small enough to work out by hand."""
+"""CPU checks of the plain-Python replays of the reference's two GPU matchers
+(Block/block_matching_online.cu:85-431, Block/block_match_cuda.cu:822-1201), on cases small enough
+to work out by hand."""
 import numpy as np
 
 from oracle import oracle as O
@@ -52,3 +53,32 @@ def test_columns_beyond_the_table_are_lost():
     assert d["fine_fb"] == 0 and d["coarse_fb_cols"] == 2048
     assert d["num_tc_blocks"] == 256 and d["dense_to_sptc_cols"] == 0
     assert d["total_nnz"] == 3000
+
+
+def test_cuda_rules_four_disjoint_columns():
+    rows = [[r // 4] for r in range(16)]
+    d = O.match_cuda_emulation(*_csr(rows))
+    # columns pair at overlap 0 (score 16 - 4), the two pairs do not conflict: one group, every row
+    # holds one of the four columns and is padded by one
+    assert d["num_groups"] == 1 and d["fine_fallback"] == 0 and d["coarse_fallback"] == 0
+    assert d["fake_zeros"] == 16
+    assert d["num_16x16_blocks"] == 1 and d["block_padding_groups"] == 3
+    assert d["num_row_panels"] == 1 and d["total_cols"] == 4
+
+
+def test_cuda_rules_prefer_the_denser_partner_and_allow_overlap():
+    # column 0: rows 0-3; column 1: rows 0-1 (overlap 2); column 2: rows 8-15 (overlap 0, 8 non-zeros)
+    rows = [[0, 1], [0, 1], [0], [0]] + [[] for _ in range(4)] + [[2] for _ in range(8)]
+    d = O.match_cuda_emulation(*_csr(rows))
+    # whatever the compaction order, a zero-overlap partner beats an overlapping one, and the odd
+    # column stays alone: two "pairs", grouped if they do not conflict
+    assert d["fine_fallback"] == 1
+    assert d["num_groups"] in (1, 2)
+    assert d["total_nnz"] + d["fake_zeros"] <= d["num_groups"] * 32
+
+
+def test_cuda_rules_lonely_window():
+    rows = [[7]] + [[] for _ in range(15)]
+    d = O.match_cuda_emulation(*_csr(rows))
+    assert d["num_groups"] == 1 and d["fine_fallback"] == 1 and d["coarse_fallback"] == 2
+    assert d["fake_zeros"] == 1 + 2 * 15      # row 0 holds one column, the other 15 rows none

@@ -8,6 +8,9 @@
 //              (the dual-routing rules of variant 0 over the columns in the SLOT ORDER of the
 //              reference's 2048-entry open-addressing table, for the schedule in which the window's
 //              rows insert one after the other; at most 2048 distinct columns per window survive)
+//   variant 4  matching_utils_cuda.match_2to4          TR-source/Block/block_match_cuda.cu:822-1201, 1216-1612
+//              (best-score pairing and grouping over the columns in the compaction order of the
+//              reference's per-window hash table, for the schedule in which its warps run one at a time)
 //
 // All three are greedy first-fit scans over the window's columns (sorted by column id) and then
 // over the pairs they produced; every step depends on which columns earlier steps consumed, so a
@@ -516,6 +519,155 @@ __global__ void km_online_counts(const int* __restrict__ begin, int W, int* __re
     int w = blockIdx.x * blockDim.x + threadIdx.x;
     if (w <= W) cnt[w] = w < W ? min(begin[w + 1] - begin[w], kOnlineSlots) : 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant 4: matching_utils_cuda.match_2to4 (TR-source/Block/block_match_cuda.cu:822-1201).
+// The reference builds, per window, an open-addressing table of 2 x window_nnz slots in global
+// memory (home slot = col * 2654435761 mod 2^32 mod size, linear probing, :861-880), compacts it
+// thread by thread - thread t of a block of T threads owns the slots t, t + T, ..., so the
+// compacted order is (slot mod T, slot) with T = 64 for windows of at most 512 non-zeros and 1024
+// otherwise (:883-927, 1284-1306, 1495-1506) - and then lets the warps of the block race for the
+// columns and for the pairs (:949-1201).  Restated here for one schedule the reference can take:
+// the entries of the window are inserted in ascending column order (an interleaving of the row
+// threads that keeps every thread's own CSR order, for rows with ascending columns), and one warp
+// at a time takes the next column / pair index from the shared counter, so every claim succeeds.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) km_cuda_order(WinCols wc, const int* __restrict__ rec_col,
+                                                     const int* __restrict__ rowptr, int n_rows, int window, int W,
+                                                     int* __restrict__ table, unsigned short* __restrict__ out_mask) {
+    __shared__ int cnt_s[4][1024];
+    const int wslot = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int w = blockIdx.x * 4 + wslot;
+    if (w >= W) return;
+    const int b = wc.begin[w], n = wc.begin[w + 1] - b;
+    if (n == 0) return;
+    const int r0 = w * window, r1 = min(r0 + window, n_rows);
+    const int e0 = rowptr[r0], wnnz = rowptr[r1] - e0;
+    const unsigned hs = (unsigned)wnnz << 1;
+    int* tab = table + ((size_t)e0 << 1);           // zero-filled: record index + 1
+    const int T = wnnz <= 512 ? 64 : 1024;
+    int* cnt = cnt_s[wslot];
+    for (int i = lane; i < T; i += 32) cnt[i] = 0;
+    if (lane == 0) {
+        for (int j = 0; j < n; ++j) {
+            unsigned slot = ((unsigned)rec_col[b + j] * 2654435761u) % hs;
+            while (tab[slot] != 0) { if (++slot == hs) slot = 0; }   // n <= window_nnz < hs: a free slot exists
+            tab[slot] = j + 1;
+            ++cnt[slot % (unsigned)T];
+        }
+    }
+    __syncwarp();
+    // exclusive prefix of the per-thread counts
+    int carry = 0;
+    for (int t0 = 0; t0 < T; t0 += 32) {
+        const int v = cnt[t0 + lane];
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        cnt[t0 + lane] = carry + x - v;
+        carry += __shfl_sync(0xffffffffu, x, 31);
+    }
+    __syncwarp();
+    for (int t = lane; t < T; t += 32) {
+        int out = b + cnt[t];
+        for (unsigned slot = (unsigned)t; slot < hs; slot += (unsigned)T) {
+            const int v = tab[slot];
+            if (v != 0) out_mask[out++] = wc.mask[b + v - 1];
+        }
+    }
+}
+
+// padding of a group made of pair a and pair b (b = 0, 0 for a lone pair): every row of the window
+// holding fewer than two of the four columns is filled up to two (block_match_cuda.cu:260-280)
+__device__ __forceinline__ int cuda_fake_zeros(unsigned a1, unsigned a2, unsigned b1, unsigned b2, unsigned rowmask) {
+    const unsigned zero = ~(a2 | b2) & rowmask;
+    const unsigned one = ((a2 & ~a1 & ~b2) | (b2 & ~b1 & ~a2)) & rowmask;
+    return 2 * __popc(zero) + __popc(one);
+}
+
+__global__ void __launch_bounds__(128) km_cuda(WinCols wc, Work wk, int W, int n_rows, int window, MStats* st) {
+    const int lane = threadIdx.x & 31;
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= W) return;
+    const int b = wc.begin[w], n = wc.begin[w + 1] - b;
+    if (n == 0) return;
+    const int win_rows = min(window, n_rows - w * window);
+    const unsigned rowmask = (1u << win_rows) - 1u;
+    const unsigned short* m = wc.mask + b;
+    unsigned char* matched = wk.matched + b;
+    unsigned short *G1 = wk.pG1 + b, *G2 = wk.pG2 + b;
+    unsigned char *pn = wk.pn1 + b, *used = wk.pused + b;
+    for (int i = lane; i < n; i += 32) { matched[i] = 0; used[i] = 0; }
+    __syncwarp();
+    // 1:2 pairing (block_match_cuda.cu:949-1062): overlap of at most 12 rows, lowest
+    // overlap * 64 + (16 - nnz of the partner), lowest index on ties
+    const int sw = n > 16384 ? 64 : n > 4096 ? 128 : 512;
+    int np = 0, fine = 0;
+    for (int i = 0; i < n; ++i) {
+        if (matched[i]) continue;
+        const unsigned mi = m[i];
+        const int j_end = min(n, i + 1 + sw);
+        unsigned best = 0xffffffffu;
+        for (int j = i + 1 + lane; j < j_end; j += 32) {
+            if (matched[j]) continue;
+            const unsigned mj = m[j];
+            const int overlap = __popc(mi & mj);
+            if (overlap > 12) continue;
+            const unsigned key = ((unsigned)(overlap * 64 + 16 - __popc(mj)) << 16) | (unsigned)(j - i);
+            best = min(best, key);
+        }
+        best = __reduce_min_sync(0xffffffffu, best);
+        if (lane == 0) {
+            matched[i] = 1;
+            if (best != 0xffffffffu) {
+                const int j = i + (int)(best & 0xffffu);
+                const unsigned mj = m[j];
+                matched[j] = 1;
+                G1[np] = (unsigned short)(mi & mj); G2[np] = (unsigned short)(mi | mj);
+                pn[np] = (unsigned char)(__popc(mi) + __popc(mj));
+            } else {
+                G1[np] = 0; G2[np] = (unsigned short)mi;
+                pn[np] = (unsigned char)__popc(mi);
+            }
+        }
+        if (best == 0xffffffffu) ++fine;
+        ++np;
+        __syncwarp();
+    }
+    // 2:4 grouping (block_match_cuda.cu:1086-1201): no row with more than two of the four columns,
+    // most non-zeros first, lowest index on ties
+    const int gw = np > 8192 ? 128 : np > 2048 ? 256 : 1024;
+    int groups = 0, coarse = 0;
+    long long fake = 0;
+    for (int i = 0; i < np; ++i) {
+        if (used[i]) continue;
+        const unsigned a1 = G1[i], a2 = G2[i];
+        const int na = pn[i];
+        const int j_end = min(np, i + 1 + gw);
+        unsigned best = 0xffffffffu;
+        for (int j = i + 1 + lane; j < j_end; j += 32) {
+            if (used[j]) continue;
+            const unsigned b1 = G1[j], b2 = G2[j];
+            if ((a1 & b2) | (a2 & b1)) continue;
+            const unsigned key = ((unsigned)(64 - (na + (int)pn[j])) << 16) | (unsigned)(j - i);
+            best = min(best, key);
+        }
+        best = __reduce_min_sync(0xffffffffu, best);
+        ++groups;
+        if (best != 0xffffffffu) {
+            const int j = i + (int)(best & 0xffffu);
+            fake += cuda_fake_zeros(a1, a2, G1[j], G2[j], rowmask);
+            if (lane == 0) used[j] = 1;
+        } else {
+            coarse += 2;
+            fake += cuda_fake_zeros(a1, a2, 0u, 0u, rowmask);
+        }
+        if (lane == 0) used[i] = 1;
+        __syncwarp();
+    }
+    if (lane == 0) flush_window(st, groups, fake, fine, coarse);
+}
+
 __global__ void km_narrow(const unsigned* __restrict__ mask32, int D, unsigned short* __restrict__ mask16) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j < D) mask16[j] = (unsigned short)mask32[j];
@@ -557,7 +709,7 @@ int bits_needed(long long max_value) { int b = 1; while ((1ll << b) <= max_value
 extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32_t* col, int n_rows, int window,
                                  int dense_threshold, int t_max, void* stream, trs_match_stats* out) {
     if (!rowptr || !out || n_rows <= 0) return TRS_E_ARG;
-    if (variant < 0 || variant > 3) return TRS_E_ARG;
+    if (variant < 0 || variant > 4) return TRS_E_ARG;
     if (window <= 0 || window > 16) return TRS_E_WINDOW;
     if ((variant == 0 || variant == 3) && (dense_threshold <= 0 || t_max < 0)) return TRS_E_ARG;
     if (variant == 3 && window != 16) return TRS_E_WINDOW;   // the reference kernel fixes 16 rows per window
@@ -636,7 +788,7 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
     TRS_CUDA(cudaMemsetAsync(mask32, 0, sizeof(unsigned) * (size_t)D, st));
     TRS_CUDA(cudaMemsetAsync(win_ncol, 0, sizeof(int) * ((size_t)W + 1), st));
     int* rec_col = nullptr;
-    if (variant == 3) M_TRY(bag.get<int>(D, &rec_col));
+    if (variant == 3 || variant == 4) M_TRY(bag.get<int>(D, &rec_col));
     km_records<<<gridm(nnz), 256, 0, st>>>(keys, head, incl, nnz, col_bits, mask32, win_ncol, rec_col);
     km_narrow<<<gridm(D), 256, 0, st>>>(mask32, D, mask16);
     TRS_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, need, win_ncol, begin, W + 1, st));
@@ -678,6 +830,15 @@ extern "C" int trs_match24_stats(int variant, const int32_t* rowptr, const int32
         km_online_order<<<gridm(W, 4), 128, 0, st>>>(wc, rec_col, W, begin2, mask2);
         WinCols wc2{begin2, mask2};
         km_para_dr<<<blocks, 128, 0, st>>>(wc2, wk, W, n_rows, window, dense_threshold, t_max, 16, d_stats);
+    } else if (variant == 4) {
+        int* table;
+        unsigned short* mask2;
+        M_TRY(bag.get<int>((size_t)nnz * 2, &table));
+        M_TRY(bag.get<unsigned short>(D, &mask2));
+        TRS_CUDA(cudaMemsetAsync(table, 0, sizeof(int) * (size_t)nnz * 2, st));
+        km_cuda_order<<<gridm(W, 4), 128, 0, st>>>(wc, rec_col, rowptr, n_rows, window, W, table, mask2);
+        WinCols wc2{begin, mask2};
+        km_cuda<<<blocks, 128, 0, st>>>(wc2, wk, W, n_rows, window, d_stats);
     } else if (variant == 1) {
         // columns of every window ordered by (mask, index): stable sort of (window, mask) keys
         u64 *mk_a, *mk_b;

@@ -231,88 +231,18 @@ __global__ void ksp_fill(const unsigned long long* __restrict__ key, const int* 
     }
 }
 
-constexpr int kSddmmBlocksPerWarp = 64;
+constexpr int kSddmmBlocksPerWarp = 48;
 
-// One warp walks kSddmmBlocksPerWarp consecutive blocks, one block at a time, with an explicit
-// pipeline: the column ids run two blocks ahead of the MMAs and the Y rows one block, so the two
-// dependent loads of a block (its record, then the rows the record names) overlap with the
-// previous blocks' work at a cost of 9 registers.  MINB holds the register allocation to MINB CTAs
-// of 128 threads per SM: many light warps measured faster than deeper per-warp unrolls (four or
-// eight blocks of Y rows requested at once cost 90-122 registers and ran 20-40 % slower).
-template <int KCH, int MINB>
-__global__ void __launch_bounds__(128, MINB) k_sddmm_tc_pipe(const SddmmBlock* __restrict__ blk, long long n_blocks,
-                                                             const __half* __restrict__ X, const __half* __restrict__ Y,
-                                                             __half* __restrict__ out, int n_rows, int blocks_per_warp) {
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long b0 = warp * blocks_per_warp;
-    if (b0 >= n_blocks) return;
-    const long long b1 = min(b0 + (long long)blocks_per_warp, n_blocks);
-    constexpr int ROW16 = KCH * 4;
-    const uint4* Xq = (const uint4*)X + t;
-    const uint4* Yq = (const uint4*)Y + t;
-
-    int cur_w = -1;
-    uint4 xa[KCH], xb[KCH], yn[KCH];
-#pragma unroll
-    for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
-
-    auto col_of = [&](long long b) { return b < b1 ? max(__ldg(&blk[b].col[g]), 0) : 0; };
-    int c_next = col_of(b0 + 1);
-    {
-        const int c0 = col_of(b0);
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) yn[ch] = __ldg(Yq + (size_t)c0 * ROW16 + ch * 4);
-    }
-    for (long long bb = b0; bb < b1; ++bb) {
-        uint4 y[KCH];
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) y[ch] = yn[ch];
-        if (bb + 1 < b1) {
-#pragma unroll
-            for (int ch = 0; ch < KCH; ++ch) yn[ch] = __ldg(Yq + (size_t)c_next * ROW16 + ch * 4);
-        }
-        c_next = col_of(bb + 2);
-        const SddmmBlock* b = blk + bb;
-        const int w = __ldg(&b->window);
-        const unsigned wa = __ldg(&b->bits[g >> 2]), wb = __ldg(&b->bits[(g >> 2) + 2]);
-        if (w != cur_w) {  // warp-uniform
-            cur_w = w;
-            const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
-#pragma unroll
-            for (int ch = 0; ch < KCH; ++ch) {
-                xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
-                xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
-            }
-        }
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) {
-            mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y[ch].x, y[ch].y);
-            mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y[ch].z, y[ch].w);
-        }
-        const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
-        const int n0 = 2 * t;
-        if ((ba >> n0) & 3u) {
-            const int s = __ldg(&b->start[g]) + __popc(ba & ((1u << n0) - 1u));
-            if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
-            if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
-        }
-        if ((bbits >> n0) & 3u) {
-            const int s = __ldg(&b->start[g + 8]) + __popc(bbits & ((1u << n0) - 1u));
-            if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
-            if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
-        }
-    }
-}
-
-// The same walk with both dependent loads of a block taken off the warp's critical path: the
+// One warp walks kSddmmBlocksPerWarp consecutive blocks, one block at a time, with both dependent
+// loads of a block taken off the warp's critical path: the
 // 128-byte records run kRecAhead blocks ahead and the 8 gathered Y rows kRowAhead blocks ahead,
 // all as 16-byte cp.async copies into the warp's own rings in shared memory (one commit group per
-// block, lanes meet in one __syncwarp per block, no block-wide barrier).  A Y row lands with its
-// 16-byte chunks rotated by the row number (chunk c of row r at position c ^ r), which makes the
-// fragment reads - lane (g, t) takes chunks 4 ch + t of row g - conflict-free without padding.
+// block, lanes meet in one __syncwarp per block, no block-wide barrier).  The odd Y rows land with
+// the two 64-byte halves of every 128 bytes swapped (chunk c at position c ^ 4): a 16-byte access
+// is served eight lanes at a time, those are the lanes (g, t) of two consecutive rows g with four
+// chunks each, and the swap puts the two rows into different halves of the 128-byte bank line, so
+// the copies and the fragment reads - lane (g, t) takes chunks 4 ch + t of row g - are
+// conflict-free without padding (rows of 64 bytes already alternate halves).
 constexpr int kRecRing = 8, kRecAhead = 6, kRowAhead = 3, kRowStages = 4;
 
 template <int KCH>
@@ -355,7 +285,7 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
 #pragma unroll
         for (int i = 0; i < KCH; ++i) {
             const int chunk = t + 4 * i;
-            cp_async16(dst + ((chunk ^ g) & (R::CPR - 1)) * 16, src + chunk, c >= 0 ? 16 : 0);
+            cp_async16(dst + ((chunk ^ ((g & 1) << 2)) & (R::CPR - 1)) * 16, src + chunk, c >= 0 ? 16 : 0);
         }
     };
     // group accounting: prologue = records 0 .. kRecAhead-1 (waited for), then one group per block j
@@ -399,7 +329,7 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
         float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ch = 0; ch < KCH; ++ch) {
-            const uint4 y = *(const uint4*)(yrow + (((4 * ch + t) ^ g) & (R::CPR - 1)) * 16);
+            const uint4 y = *(const uint4*)(yrow + (((4 * ch + t) ^ ((g & 1) << 2)) & (R::CPR - 1)) * 16);
             mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y.x, y.y);
             mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y.z, y.w);
         }
@@ -558,25 +488,20 @@ extern "C" int trs_sddmm_plan_run(const trs_sddmm_plan* p, const trs_half* X, co
     const bool tc = (K == 32 || K == 64 || K == 128) && (((uintptr_t)X & 15) == 0) && (((uintptr_t)Y & 15) == 0);
     if (!tc) return trs_sddmm(p->rowptr, p->col, X, Y, out, p->n_rows, p->n_cols, K, stream);
     cudaStream_t st = (cudaStream_t)stream;
-    static const int bpw = [] { const char* v = getenv("TRS_SDDMM_BPW"); return v && atoi(v) > 0 ? atoi(v) : trs::kSddmmBlocksPerWarp; }();
+    const int bpw = trs::kSddmmBlocksPerWarp;
     const long long warps = trs::ceil_div64(p->n_blocks, bpw);
     const unsigned grid = (unsigned)trs::ceil_div64(warps, 4);
     const __half *x = (const __half*)X, *y = (const __half*)Y;
-    static const bool ring = [] { const char* v = getenv("TRS_SDDMM_KERNEL"); return !(v && strcmp(v, "pipe") == 0); }();
-    if (ring) {
-        auto launch = [&](auto kernel, int smem) -> int {
-            TRS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            kernel<<<grid, 128, smem, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-            return TRS_OK;
-        };
-        int rc;
-        if (K == 32) rc = launch(trs::k_sddmm_tc_ring<1, 8>, trs::SddmmRing<1>::SMEM);
-        else if (K == 64) rc = launch(trs::k_sddmm_tc_ring<2, 8>, trs::SddmmRing<2>::SMEM);
-        else rc = launch(trs::k_sddmm_tc_ring<4, 5>, trs::SddmmRing<4>::SMEM);
-        if (rc) return rc;
-    } else if (K == 32) trs::k_sddmm_tc_pipe<1, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-    else if (K == 64) trs::k_sddmm_tc_pipe<2, 8><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
-    else trs::k_sddmm_tc_pipe<4, 5><<<grid, 128, 0, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+    auto launch = [&](auto kernel, int smem) -> int {
+        TRS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kernel<<<grid, 128, smem, st>>>(p->blocks.p, p->n_blocks, x, y, (__half*)out, p->n_rows, bpw);
+        return TRS_OK;
+    };
+    int rc;
+    if (K == 32) rc = launch(trs::k_sddmm_tc_ring<1, 8>, trs::SddmmRing<1>::SMEM);
+    else if (K == 64) rc = launch(trs::k_sddmm_tc_ring<2, 8>, trs::SddmmRing<2>::SMEM);
+    else rc = launch(trs::k_sddmm_tc_ring<4, 5>, trs::SddmmRing<4>::SMEM);
+    if (rc) return rc;
     TRS_LAUNCH_CHECK();
     return TRS_OK;
 }

@@ -432,10 +432,15 @@ __global__ void __launch_bounds__(WARPS * 32) k_window_spmm(const KernelArgs a) 
 // ----------------------------------------------------------------------------------------------
 // FS = features per warp (32 / 64 / 128; F > FS adds feature slabs on gridDim.y).  Per k-step the
 // warp copies the 16 gathered rows (FS * 2 bytes each) with 16 / (256 / FS) cp.async instructions
-// of 16 bytes per lane into a stage of its own ring (row pitch FS * 2 + 16 bytes: conflict-free
-// ldmatrix), the A operand (256 B packed values + 32 B metadata, or two expanded TC blocks) into
-// the same stage, and the column ids of a later step into a small id ring.  Commit groups give the
-// ordering (see the group accounting at the loop); lanes meet in one __syncwarp per step.
+// of 16 bytes per lane into a stage of its own ring - rows unpadded, the 16-byte chunks of a row
+// swizzled by the row number so that ldmatrix is conflict-free - and the column ids of a later
+// step into a small id ring.  The A operand (8 bytes of packed values and one metadata word per
+// lane, or the four fragment words of two expanded TC blocks) is a coalesced stream read once; it
+// goes straight into registers STAGES - 1 steps ahead, so the ring holds gathered rows only:
+// 3 x 4 KB + 256 B per warp at FS = 128, which lets 16 one-warp CTAs (four per scheduler, 128
+// registers each) share an SM - shared memory would take 17, but the fifth warp of one scheduler
+// would cap every warp at 96 registers, which measured slower.  Commit groups give the ordering
+// (see the group accounting at the loop); lanes meet in one __syncwarp per step.
 // Requirements (checked by the launcher): F % 8 == 0, B / C / scratch and the tile arrays 16-byte
 // aligned.
 template <int FS, int STAGES>
@@ -444,14 +449,16 @@ struct WarpTile {
     static constexpr int CPR = FS / 8;              // 16-byte chunks per gathered row
     static constexpr int RPI = 32 / CPR;            // rows one cp.async warp-instruction covers
     static constexpr int NCP = 16 / RPI;            // cp.async instructions per lane and step
-    static constexpr int ROWB = FS * 2 + 16;
-    static constexpr int BBYTES = 16 * ROWB;
-    static constexpr int STAGE = BBYTES + 512;      // + A operand
-    static constexpr int RING = 8;                  // id ring slots (64 B each), > 2 * STAGES - 2
+    static constexpr int ROWB = FS * 2;             // no padding: the chunks of a row are swizzled
+    static constexpr int STAGE = 16 * ROWB;         // the B rows only; the A operand rides in registers
     static constexpr int IDA = 2 * STAGES - 2;      // ids run this many steps ahead
+    static constexpr int RING = IDA <= 4 ? 4 : 8;   // id ring slots (64 B each), >= max(STAGES, IDA)
     static constexpr int SMEM = STAGE * STAGES + RING * 64;
     static_assert(STAGES >= 2 && STAGES <= 4, "id ring holds 8 steps");
     static_assert(SMEM >= 16 * (FS * 4 + 16), "the epilogue stages a 16 x FS fp32 tile in the ring");
+    // chunk c of row r sits at position c ^ swz(r): the 8 rows one ldmatrix phase reads land in 8
+    // different 16-byte bank groups (rows of 64 B share a 128-byte line in pairs)
+    __device__ static constexpr int swz(int r) { return FS == 32 ? ((r >> 1) & 3) : (r & 7); }
 };
 
 // Adds the item's CSR remainder parts into a zeroed 16 x FS fp32 tile in shared memory.  A group
@@ -641,10 +648,13 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
     const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;    // this lane's chunk inside a row
     const bool fin = fbase + ch * 8 < a.F;
     const uint4* Bq = (const uint4*)a.B;
-    const uint32_t dst0 = smem0 + (sub * T::NCP) * T::ROWB + ch * 16;
+    const uint32_t dst0 = smem0 + (sub * T::NCP) * T::ROWB;
     // ldmatrix role: matrix lane / 8 -> k rows (m & 1) * 8 .., features (m >> 1) * 8 ..
     const int mtx = lane >> 3;
-    const uint32_t boff = smem0 + ((lane & 7) + (mtx & 1) * 8) * T::ROWB + ((mtx >> 1) * 8) * 2;
+    const int lrow = (lane & 7) + (mtx & 1) * 8;
+    const uint32_t boff = smem0 + lrow * T::ROWB;
+    const int lswz = T::swz(lrow), lchunk = mtx >> 1;
+    const int t = lane & 3;
 
     float acc[T::NT][4];
 #pragma unroll
@@ -684,47 +694,52 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
 #pragma unroll
         for (int k = 0; k < T::NCP; ++k) {
             const uint32_t o = (uint32_t)max(c[k], 0) * pitch16 + chunk16;
-            cp_async16(d + k * T::ROWB, Bq + o, (c[k] >= 0 && fin) ? 16 : 0);
-        }
-        // A operand
-        const int s = it.step_begin + j;
-        const uint32_t adst = smem0 + stage * T::STAGE + T::BBYTES + lane * 16;
-        if (s < it.ntiles) {
-            const size_t tile = (size_t)(it.tile0 + s);
-            if (lane < 16) cp_async16(adst, a.f.s_packed_a + tile * 64 + lane * 4, 16);
-            else if (lane < 18) cp_async16(adst, a.f.s_packed_meta + tile * 8 + (lane - 16) * 4, 16);
-        } else {
-            const int b = it.blk0 + 2 * (s - it.ntiles) + (lane >> 4);
-            const bool live = b < it.blk_end;
-            cp_async16(adst, a.tc_dense + (size_t)(live ? b : it.blk0) * 128 + (lane & 15) * 8, live ? 16 : 0);
+            cp_async16(d + k * T::ROWB + ((ch ^ T::swz(sub * T::NCP + k)) << 4), Bq + o, (c[k] >= 0 && fin) ? 16 : 0);
         }
     };
 
-    auto compute = [&](int j, int stage) {
-        const unsigned char* as = smem + stage * T::STAGE + T::BBYTES;
+    // A operand of step j, straight into registers (a coalesced stream, read once): a packed tile
+    // gives this lane its 8 bytes of values (x, y) and its metadata word (z); a pair of TC blocks
+    // gives the four fragment words of the dense 16 x 16 tile
+    auto load_a = [&](int j) -> uint4 {
+        uint4 r = make_uint4(0u, 0u, 0u, 0u);
+        if (j >= nsteps) return r;
+        const int s = it.step_begin + j;
+        if (s < it.ntiles) {
+            const size_t tile = (size_t)(it.tile0 + s);
+            const uint2 v = __ldg((const uint2*)(a.f.s_packed_a + tile * 64) + lane);
+            r.x = v.x; r.y = v.y;
+            r.z = (uint32_t)__ldg(a.f.s_packed_meta + tile * 8 + g);
+        } else {
+            const int b = it.blk0 + 2 * (s - it.ntiles);
+            const uint32_t* d0 = (const uint32_t*)(a.tc_dense + (size_t)b * 128);
+            r.x = __ldg(d0 + g * 4 + t);
+            r.y = __ldg(d0 + (g + 8) * 4 + t);
+            if (b + 1 < it.blk_end) {
+                r.z = __ldg(d0 + 64 + g * 4 + t);
+                r.w = __ldg(d0 + 64 + (g + 8) * 4 + t);
+            }
+        }
+        return r;
+    };
+
+    auto compute = [&](int j, int stage, const uint4& av) {
         const uint32_t baddr = boff + stage * T::STAGE;
         if (j < nsparse) {
-            const uint2 av = *(const uint2*)(as + lane * 8);
-            const uint32_t meta = *(const uint32_t*)(as + 256 + g * 4);
 #pragma unroll
             for (int h = 0; h < T::NT / 2; ++h) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, meta);
-                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, meta);
+                ldmatrix_x4_trans(baddr + (((2 * h + lchunk) ^ lswz) << 4), b0, b1, b2, b3);
+                mma_sp_16816(acc[2 * h], av.x, av.y, b0, b1, av.z);
+                mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, av.z);
             }
         } else {
-            const int t = lane & 3;
-            const uint32_t a0 = *(const uint32_t*)(as + g * 16 + t * 4);
-            const uint32_t a1 = *(const uint32_t*)(as + (g + 8) * 16 + t * 4);
-            const uint32_t a2 = *(const uint32_t*)(as + 256 + g * 16 + t * 4);
-            const uint32_t a3 = *(const uint32_t*)(as + 256 + (g + 8) * 16 + t * 4);
 #pragma unroll
             for (int h = 0; h < T::NT / 2; ++h) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(baddr + h * 32, b0, b1, b2, b3);
-                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
-                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
+                ldmatrix_x4_trans(baddr + (((2 * h + lchunk) ^ lswz) << 4), b0, b1, b2, b3);
+                mma_16816(acc[2 * h], av.x, av.y, av.z, av.w, b0, b1);
+                mma_16816(acc[2 * h + 1], av.x, av.y, av.z, av.w, b2, b3);
             }
         }
     };
@@ -739,10 +754,12 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
     cp_async_commit();
     cp_async_wait<0>();
     __syncwarp();
+    uint4 areg[STAGES];
 #pragma unroll
     for (int j = 0; j < STAGES - 1; ++j) {
         if (j < nsteps) issue(j, j);
         cp_async_commit();
+        areg[j] = load_a(j);
     }
     for (int j0 = 0; j0 < nsteps; j0 += STAGES) {
 #pragma unroll
@@ -754,7 +771,8 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
                 issue_idx(j + T::IDA);
                 if (j + STAGES - 1 < nsteps) issue(j + STAGES - 1, (u + STAGES - 1) % STAGES);
                 cp_async_commit();
-                compute(j, u);
+                areg[(u + STAGES - 1) % STAGES] = load_a(j + STAGES - 1);
+                compute(j, u, areg[u]);
             }
         }
     }

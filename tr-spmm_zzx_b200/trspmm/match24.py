@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 
-VARIANTS = {"para_dr": 0, "hash": 1, "bucket": 2, "online": 3}
+VARIANTS = {"para_dr": 0, "hash": 1, "bucket": 2, "online": 3, "cuda": 4}
 
 
 class TrsMatchStats(C.Structure):
