@@ -40,7 +40,7 @@ sys.path.insert(0, str(ROOT))
 import torch  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
-LEG_NAMES = ("h2d_ms", "allgather_ms", "kernel_ms", "d2h_ms")
+LEG_NAMES = ("h2d_ms", "allgather_ms", "kernel_ms", "redeal_ms", "d2h_ms")
 
 WORKLOADS = {
     # name: (generator, kwargs, F)
@@ -447,12 +447,14 @@ def run_ours(args, rank, world, local_rank):
                     "B host->device and C device->host; consecutive steps overlap on three streams)")
         e2e_block_call = "trs_resident_forward, one blocking call per step"
     else:
-        # every rank copies its 1/N slice of B over PCIe, the slices are all-gathered over NVLink,
-        # each rank multiplies its windows and copies its rows of C back
-        sh = shard.ShardedHostSpmm(fmt, m_local, n, F, rank, world)
+        # every rank copies its 1/N slice of B over PCIe, the slices are exchanged over NVLink, each
+        # rank multiplies its windows, the computed rows are re-dealt over NVLink so that every rank
+        # copies the same 1/N of C back (the cost-balanced cut gives the ranks very different row counts)
+        sh = shard.ShardedHostSpmm(fmt, m_local, n, F, rank, world, row_cuts=cuts, exchange=args.exchange)
         k0, k1 = sh.my_rows()
+        o0, o1 = sh.out_rows()
         B_hosts = [B[k0:k1].cpu().pin_memory() for _ in range(2)]
-        C_hosts = [torch.empty((max(m_local, 1), F), dtype=torch.float16).pin_memory() for _ in range(2)]
+        C_hosts = [torch.empty((o1 - o0, F), dtype=torch.float16).pin_memory() for _ in range(2)]
         for i in range(2):
             sh.submit(B_hosts[i], C_hosts[i])
         sh.wait()
@@ -469,11 +471,26 @@ def run_ours(args, rank, world, local_rank):
         sh.wait()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
         legs = sh.leg_ms()
-        e2e_call = (f"ShardedHostSpmm.submit x steps + wait: each rank copies 1/{world} of B host->device, NCCL "
-                    "all-gather over NVLink, own windows, own rows of C device->host; steps overlap on four streams")
+        e2e_call = (f"ShardedHostSpmm.submit x steps + wait: each rank copies 1/{world} of B host->device, "
+                    f"{'NCCL all-gather' if args.exchange == 'nccl' else 'copy-engine pushes'} over NVLink, own windows, "
+                    f"computed rows re-dealt over NVLink, 1/{world} of C device->host; steps overlap on five streams")
         e2e_block_call = "ShardedHostSpmm.submit + wait per step"
-    if not torch.equal(C_hosts[0], C_hosts[1]) or not torch.equal(C_hosts[0], out.cpu()):
-        raise RuntimeError("host-buffer calls disagree with the device-resident result")
+    if world == 1:
+        if not torch.equal(C_hosts[0], C_hosts[1]) or not torch.equal(C_hosts[0], out.cpu()):
+            raise RuntimeError("host-buffer calls disagree with the device-resident result")
+    else:
+        # the rows this rank delivered against the device-resident results of the ranks that computed them
+        full = torch.empty((n, F), dtype=torch.float16, device=dev)
+        for r in range(world):
+            piece = full[cuts[r]:cuts[r + 1]]
+            if r == rank and m_local > 0:
+                piece.copy_(out[:m_local])
+            if piece.numel():
+                dist.broadcast(piece, src=r)
+        want = full[o0:o1].cpu()
+        if not torch.equal(C_hosts[0], C_hosts[1]) or not torch.equal(C_hosts[0], want):
+            raise RuntimeError("host-buffer calls disagree with the device-resident result")
+        del full, want
 
     kept = torch.tensor([float(kept_local), ms, e2e_ms, e2e_sync_ms, p_max, p_mean, float(p_rows)], device=dev,
                         dtype=torch.float64)
@@ -524,6 +541,7 @@ def run_ours(args, rank, world, local_rank):
                     "h2d_ms": h2d / e2e_steps if world == 1 else legs["h2d_ms"],
                     "d2h_ms": d2h / e2e_steps if world == 1 else legs["d2h_ms"],
                     "allgather_ms": legs["allgather_ms"], "kernel_ms": legs["kernel_ms"] if world > 1 else ms,
+                    "redeal_ms": legs["redeal_ms"],
                     "legs": "device time of each leg of the last streamed call, max over ranks" if world > 1 else
                             "copy legs of the blocking calls (trs_timing)",
                     "steps": e2e_steps, "numa_node_rank0": numa_node,
@@ -858,6 +876,8 @@ def main():
                     help="spmm: lossless format (no dropped entries; value counts all nnz) - a separate, labelled configuration")
     ap.add_argument("--op", default="spmm", choices=["spmm", "sddmm", "gcn", "build", "match24"],
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "push"],
+                    help="multi-GPU host-buffer path: how the ranks exchange their slices of B")
     ap.add_argument("--gather", default="push", choices=["h1", "z2", "fused", "push"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -24,23 +24,36 @@ def main():
     rp, col, val = rp[: n + 1].to(dev), col[: int(rp[n])].to(dev), val[: int(rp[n])].to(dev)
     n_cols = rp.numel() - 1 + 5
     F = 64
-    (r0, r1), (rp_l, col_l, val_l) = shard.shard_for_rank(rp, col, val, rank, world)
+    cuts = shard.balanced_window_cuts(rp, world)
+    r0, r1 = cuts[rank], cuts[rank + 1]
+    rp_l, col_l, val_l = shard.slice_csr(rp, col, val, r0, r1)
     fmt, _ = build_format(rp_l, col_l, val_l)
     full_fmt, _ = build_format(rp, col, val)
-    sh = shard.ShardedHostSpmm(fmt, r1 - r0, n_cols, F, rank, world)
-    k0, k1 = sh.my_rows()
+    plan = SpmmPlan(full_fmt, n, n_cols)
     ok = True
     g = torch.Generator().manual_seed(11)
     Bs = [torch.randn(n_cols, F, generator=g).half() for _ in range(5)]      # identical on every rank (same seed)
-    outs = [torch.full((max(r1 - r0, 1), F), float("nan"), dtype=torch.float16).pin_memory() for _ in Bs]
-    slices = [b[k0:k1].clone().pin_memory() for b in Bs]
-    for sl, o in zip(slices, outs):
-        sh.submit(sl, o)
-    sh.wait()
-    plan = SpmmPlan(full_fmt, n, n_cols)
-    for b, o in zip(Bs, outs):
-        want = plan.run(b.to(dev), out_dtype=torch.float16)[r0:r1].cpu()
-        ok = ok and bool(torch.equal(o[: r1 - r0], want))
+    wants = [plan.run(b.to(dev), out_dtype=torch.float16).cpu() for b in Bs]
+    # the rank's computed rows / an even share of the rows re-dealt over NVLink, NCCL / copy-engine exchange of B
+    for row_cuts, exchange in ((None, "nccl"), (cuts, "nccl"), (cuts, "push")):
+        if world == 1 and row_cuts is not None:
+            continue
+        sh = shard.ShardedHostSpmm(fmt, r1 - r0, n_cols, F, rank, world, row_cuts=row_cuts, exchange=exchange)
+        k0, k1 = sh.my_rows()
+        o0, o1 = (r0, r1) if row_cuts is None else sh.out_rows()
+        if row_cuts is not None:
+            assert (o0, o1) == shard.even_output_rows(n, world, rank)
+        rows = max(r1 - r0, 1) if row_cuts is None else o1 - o0
+        outs = [torch.full((rows, F), float("nan"), dtype=torch.float16).pin_memory() for _ in Bs]
+        slices = [b[k0:k1].clone().pin_memory() for b in Bs]
+        for sl, o in zip(slices, outs):
+            sh.submit(sl, o)
+        sh.wait()
+        for want, o in zip(wants, outs):
+            ok = ok and bool(torch.equal(o[: o1 - o0], want[o0:o1]))
+        legs = sh.leg_ms()
+        ok = ok and all(v >= 0.0 for v in legs.values())
+        del sh
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.barrier()

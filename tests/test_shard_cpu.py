@@ -163,3 +163,29 @@ def test_rescale_costs_moves_windows_away_from_the_slow_rank():
     assert all(c % 16 == 0 for c in new_cuts)
     # equal times change nothing
     assert cuts_from_window_costs(rescale_costs(cost, cuts, [2.0] * 4), 4, n) == cuts
+
+
+def test_output_transfers_cover_every_even_share_exactly_once():
+    """Re-deal of the computed rows: for any cut, the pieces the ranks send to a peer tile that
+    peer's even share of the rows without gap or overlap."""
+    import random
+    rng = random.Random(5)
+    for world in (2, 3, 8):
+        for n in (1, 17, 1000, 4099):
+            for _ in range(20):
+                inner = sorted(rng.randint(0, n) for _ in range(world - 1))
+                cuts = [0] + inner + [n]
+                got = {p: [] for p in range(world)}
+                for r in range(world):
+                    for peer, src, dst, cnt in shard.output_transfers(cuts, r):
+                        assert cnt > 0 and 0 <= src and src + cnt <= cuts[r + 1] - cuts[r]
+                        o0, o1 = shard.even_output_rows(n, world, peer)
+                        assert cuts[r] + src == o0 + dst         # the same global row on both sides
+                        got[peer].append((dst, cnt))
+                for p in range(world):
+                    o0, o1 = shard.even_output_rows(n, world, p)
+                    pos = 0
+                    for dst, cnt in sorted(got[p]):
+                        assert dst == pos
+                        pos += cnt
+                    assert pos == o1 - o0

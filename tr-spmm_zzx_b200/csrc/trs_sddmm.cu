@@ -242,7 +242,9 @@ constexpr int kSddmmBlocksPerWarp = 48;
 // is served eight lanes at a time, those are the lanes (g, t) of two consecutive rows g with four
 // chunks each, and the swap puts the two rows into different halves of the 128-byte bank line, so
 // the copies and the fragment reads - lane (g, t) takes chunks 4 ch + t of row g - are
-// conflict-free without padding (rows of 64 bytes already alternate halves).
+// conflict-free without padding (rows of 64 bytes already alternate halves).  Holding the rows in
+// registers instead (plain 16-byte loads two blocks ahead, no shared-memory round trip) measured
+// slower: 0.127 against 0.109 ms on the clustered pattern.
 constexpr int kRecRing = 8, kRecAhead = 6, kRowAhead = 3, kRowStages = 4;
 
 template <int KCH>
@@ -348,6 +350,7 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
     }
     cp_async_wait<0>();
 }
+
 
 }  // namespace trs
 

@@ -452,7 +452,7 @@ struct WarpTile {
     static constexpr int ROWB = FS * 2;             // no padding: the chunks of a row are swizzled
     static constexpr int STAGE = 16 * ROWB;         // the B rows only; the A operand rides in registers
     static constexpr int IDA = 2 * STAGES - 2;      // ids run this many steps ahead
-    static constexpr int RING = IDA <= 4 ? 4 : 8;   // id ring slots (64 B each), >= max(STAGES, IDA)
+    static constexpr int RING = IDA <= 4 ? 4 : 8;   // id ring slots (64 B each), >= IDA
     static constexpr int SMEM = STAGE * STAGES + RING * 64;
     static_assert(STAGES >= 2 && STAGES <= 4, "id ring holds 8 steps");
     static_assert(SMEM >= 16 * (FS * 4 + 16), "the epilogue stages a 16 x FS fp32 tile in the ring");
@@ -761,6 +761,7 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
         cp_async_commit();
         areg[j] = load_a(j);
     }
+
     for (int j0 = 0; j0 < nsteps; j0 += STAGES) {
 #pragma unroll
         for (int u = 0; u < STAGES; ++u) {
@@ -1142,9 +1143,11 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     // The warp-owner kernel moves everything in 16-byte pieces; anything else takes the fallback.
     const bool aligned = p->arrays_aligned && (F % 8 == 0) &&
                          ((((uintptr_t)B | (uintptr_t)C | (uintptr_t)workspace) & 15) == 0);
-    // Three stages (two k-steps in flight per warp) measured fastest at R-MAT scale 21: 3.64 / 3.03 /
-    // 3.18 ms for 2 / 3 / 4 stages (more stages leave fewer warps per SM: shared memory is the limit);
-    // 64-feature slabs for F = 128 (24 warps per SM, twice the steps) were slower too (3.46 ms).
+    // Three stages (two k-steps in flight per warp) and 16 warps per SM (four per scheduler)
+    // measured fastest at R-MAT scale 21: 2.72 ms, against 3.16 ms for four stages (13 warps) and
+    // 3.05 ms for 17 warps of 96 registers; 64-feature slabs for F = 128 (24 warps per SM, twice
+    // the steps) were slower too, and so was asking L2 for the rows (or the packed tiles) of later
+    // steps with prefetch instructions two to four steps ahead (2.9 - 3.3 ms; bulk prefetches 4.1 ms).
     int rc;
     if (!aligned) {
         if (n_peers > 0) return TRS_E_ARG;

@@ -129,89 +129,193 @@ def bind_to_gpu_numa_node(device_index: int):
         return None
 
 
+def even_output_rows(n_rows: int, world: int, rank: int):
+    """[begin, end) rows of C that `rank` hands to the host when the output is split evenly."""
+    per = (n_rows + world - 1) // world
+    return min(rank * per, n_rows), min((rank + 1) * per, n_rows)
+
+
+def output_transfers(row_cuts, rank: int):
+    """Where the rows this rank computed go when every rank delivers an even share of C.
+
+    `row_cuts` are the computed-row boundaries of all ranks (world + 1 values).  Returns a list of
+    (peer, src_begin, dst_begin, count): `count` rows starting at local row `src_begin` of this rank's
+    result belong at row `dst_begin` of peer's output share (peer may be this rank)."""
+    world = len(row_cuts) - 1
+    n_rows = row_cuts[-1]
+    r0, r1 = row_cuts[rank], row_cuts[rank + 1]
+    moves = []
+    for peer in range(world):
+        o0, o1 = even_output_rows(n_rows, world, peer)
+        a, b = max(r0, o0), min(r1, o1)
+        if b > a:
+            moves.append((peer, a - r0, a - o0, b - a))
+    return moves
+
+
 class ShardedHostSpmm:
     """Host-buffer SpMM on `world` GPUs of one box, for a stream of calls over one matrix.
 
     Without it every rank would pull the whole dense operand B over PCIe (world copies of the same
     bytes through the host's memory system).  Here each rank copies only its 1/world slice of B
-    from pinned host memory, the slices are exchanged with one in-place NCCL all-gather over NVLink,
-    each rank multiplies its own row windows, and copies its rows of C back.  Four streams (input
-    copy, all-gather, kernels, output copy) and two buffer slots let consecutive calls overlap.
+    from pinned host memory, the slices are exchanged over NVLink (one in-place NCCL all-gather, or
+    copy-engine pushes into the peers' buffers with exchange="push"), each rank multiplies its own
+    row windows, and the result goes back to the host.  The row windows are cut by cost, so the
+    ranks compute very different numbers of rows (R-MAT at two ranks: 0.33 M against 1.77 M); with
+    `row_cuts` given, the computed rows are therefore re-dealt over NVLink first (copy-engine
+    pushes into peer-mapped buffers) so that every rank copies the same 1/world of C to its host
+    buffer and no PCIe link carries more than its share.  Five streams (input copy, exchange of B,
+    kernels, exchange of C, output copy) and two buffer slots let consecutive calls overlap.
 
     The reference has no multi-GPU path; the single-GPU call this extends is
     spmm_forward_fp16_tcu_cuda_sptc_mma_parallel_online (mGCN_online.cpp:760), which copies B in and
     C out on every call.
     """
 
-    def __init__(self, fmt, m_local: int, n_cols: int, F: int, rank: int, world: int, group=None):
+    def __init__(self, fmt, m_local: int, n_cols: int, F: int, rank: int, world: int, group=None, row_cuts=None,
+                 exchange: str = "nccl"):
         import torch.distributed as dist
         from .spmm import SpmmPlan
+        if exchange not in ("nccl", "push"):
+            raise ValueError("exchange must be 'nccl' or 'push'")
         self.dist, self.group = dist, group
         self.rank, self.world, self.F = rank, world, F
         self.m_local, self.n_cols = max(m_local, 1), n_cols
         self.dev = fmt.device
         self.plan = SpmmPlan(fmt, self.m_local, n_cols)
         self.per, padded = even_row_split(n_cols, world)
-        self.B = [torch.zeros((padded, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
+        self.exchange = exchange if world > 1 else "nccl"
+        self.row_cuts = list(row_cuts) if (row_cuts is not None and world > 1) else None
+        if self.row_cuts is not None and (len(self.row_cuts) != world + 1 or
+                                          self.row_cuts[rank + 1] - self.row_cuts[rank] != m_local):
+            raise ValueError("row_cuts do not describe this rank's rows")
+        symmetric = self.exchange == "push" or self.row_cuts is not None
+        if symmetric:
+            import torch.distributed._symmetric_memory as symm_mem
+            pg = group if group is not None else dist.group.WORLD
+        if self.exchange == "push":
+            self._Bsym = symm_mem.empty((2, padded, F), dtype=torch.float16, device=self.dev)
+            self._Bhdl = symm_mem.rendezvous(self._Bsym, group=pg)
+            self._Bsym.zero_()
+            self.B = [self._Bsym[0], self._Bsym[1]]
+            self._Bpeer = [self._Bhdl.get_buffer(p, (2, padded, F), torch.float16) for p in range(world)]
+            # PCIe copies run between pinned host memory and plain device memory only (copies to or from
+            # the peer-mapped allocations measured at half the rate): the slice lands here first
+            self._Bstage = [torch.zeros((self.per, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
+        else:
+            self.B = [torch.zeros((padded, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
         self.C = [torch.empty((self.m_local, F), dtype=torch.float16, device=self.dev) for _ in range(2)]
-        self.s_in, self.s_comm, self.s_k, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(4))
+        if self.row_cuts is not None:
+            self.out0, self.out1 = even_output_rows(self.row_cuts[-1], world, rank)
+            self.per_out = (self.row_cuts[-1] + world - 1) // world
+            self._Csym = symm_mem.empty((2, max(self.per_out, 1), F), dtype=torch.float16, device=self.dev)
+            self._Chdl = symm_mem.rendezvous(self._Csym, group=pg)
+            self._Cpeer = [self._Chdl.get_buffer(p, (2, max(self.per_out, 1), F), torch.float16) for p in range(world)]
+            self._moves = output_transfers(self.row_cuts, rank)
+            self._Cout = [torch.empty((max(self.per_out, 1), F), dtype=torch.float16, device=self.dev) for _ in range(2)]
+        hi = lambda: torch.cuda.Stream(self.dev, priority=-1)  # noqa: E731  small kernels ahead of the SpMM's queue
+        self.s_in, self.s_k, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+        self.s_comm, self.s_x = hi(), hi()
         ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
-        self.in_done, self.comm_done, self.k_done, self.out_done = ([ev(), ev()] for _ in range(4))
-        self.in_start, self.comm_start, self.k_start, self.out_start = ([ev(), ev()] for _ in range(4))
+        self.in_done, self.comm_done, self.k_done, self.x_done, self.out_done = ([ev(), ev()] for _ in range(5))
+        self.in_start, self.comm_start, self.k_start, self.x_start, self.out_start = ([ev(), ev()] for _ in range(5))
         self.seq = 0
         self._keep = []
+        if symmetric:
+            torch.cuda.synchronize(self.dev)
+            dist.barrier(group=group)
 
     def my_rows(self):
         """[begin, end) rows of B this rank is expected to provide."""
         b = self.rank * self.per
         return b, min(b + self.per, self.n_cols)
 
+    def out_rows(self):
+        """[begin, end) rows of C this rank delivers when the output is re-dealt (row_cuts given):
+        an even share of all rows.  None otherwise (the rank delivers the rows it computed)."""
+        if self.row_cuts is None:
+            return None
+        return self.out0, self.out1
+
     def submit(self, B_slice_host: torch.Tensor, C_host: torch.Tensor):
-        """B_slice_host: pinned fp16 [rows of my_rows(), F]; C_host: pinned fp16 [m_local, F]."""
+        """B_slice_host: pinned fp16 [rows of my_rows(), F]; C_host: pinned fp16, [m_local, F] or, with
+        row_cuts, [rows of out_rows(), F]."""
         s = self.seq & 1
         b0, b1 = self.my_rows()
-        if B_slice_host.shape != (b1 - b0, self.F) or C_host.shape != (self.m_local, self.F):
+        c_rows = self.m_local if self.row_cuts is None else self.out1 - self.out0
+        if B_slice_host.shape != (b1 - b0, self.F) or C_host.shape != (c_rows, self.F):
             raise ValueError("slice shapes do not match this rank's share")
         self._keep.append((B_slice_host, C_host))
         Bs, Cs = self.B[s], self.C[s]
         with torch.cuda.stream(self.s_in):
             self.s_in.wait_event(self.k_done[s])           # the kernels two calls back are done with this slot
             self.in_start[s].record(self.s_in)
-            Bs[b0:b1].copy_(B_slice_host, non_blocking=True)
+            if self.exchange == "push":
+                self._Bstage[s][:b1 - b0].copy_(B_slice_host, non_blocking=True)
+            else:
+                Bs[b0:b1].copy_(B_slice_host, non_blocking=True)
             self.in_done[s].record(self.s_in)
         with torch.cuda.stream(self.s_comm):
             self.s_comm.wait_event(self.in_done[s])
             self.comm_start[s].record(self.s_comm)
-            if self.world > 1:
+            if self.world > 1 and self.exchange == "nccl":
                 mine = Bs[self.rank * self.per:(self.rank + 1) * self.per]
                 self.dist.all_gather_into_tensor(Bs, mine, group=self.group)   # in place: `mine` is its own piece of Bs
+            elif self.world > 1:
+                # every rank's kernels two calls back are done with slot s (their input copies waited
+                # for them), then the copy engines put this rank's slice into every peer's B
+                self._Bhdl.barrier(channel=s)
+                for d in range(self.world):
+                    p = (self.rank + d) % self.world
+                    self._Bpeer[p][s, b0:b1].copy_(self._Bstage[s][:b1 - b0], non_blocking=True)
+                self._Bhdl.barrier(channel=2 + s)
             self.comm_done[s].record(self.s_comm)
         with torch.cuda.stream(self.s_k):
             self.s_k.wait_event(self.comm_done[s])
-            self.s_k.wait_event(self.out_done[s])           # the output copy two calls back has drained this slot
+            self.s_k.wait_event(self.x_done[s] if self.row_cuts is not None else self.out_done[s])  # slot's C drained
             self.k_start[s].record(self.s_k)
             self.plan.run(Bs[:self.n_cols], out=Cs)
             self.k_done[s].record(self.s_k)
+        if self.row_cuts is not None:
+            with torch.cuda.stream(self.s_x):
+                self.s_x.wait_event(self.k_done[s])
+                self.x_start[s].record(self.s_x)
+                self._Chdl.barrier(channel=s)               # every rank has moved slot s of two calls back out of the way
+                for peer, src, dst, cnt in self._moves:
+                    self._Cpeer[peer][s, dst:dst + cnt].copy_(Cs[src:src + cnt], non_blocking=True)
+                self._Chdl.barrier(channel=2 + s)           # every rank's rows have landed
+                self.s_x.wait_event(self.out_done[s])       # the output copy two calls back has read _Cout[s]
+                if c_rows > 0:
+                    self._Cout[s][:c_rows].copy_(self._Csym[s, :c_rows], non_blocking=True)   # plain memory for the PCIe copy
+                self.x_done[s].record(self.s_x)
         with torch.cuda.stream(self.s_out):
-            self.s_out.wait_event(self.k_done[s])
-            self.out_start[s].record(self.s_out)
-            C_host.copy_(Cs, non_blocking=True)
+            if self.row_cuts is not None:
+                self.s_out.wait_event(self.x_done[s])
+                self.out_start[s].record(self.s_out)
+                if c_rows > 0:
+                    C_host.copy_(self._Cout[s][:c_rows], non_blocking=True)
+            else:
+                self.s_out.wait_event(self.k_done[s])
+                self.out_start[s].record(self.s_out)
+                C_host.copy_(Cs, non_blocking=True)
             self.out_done[s].record(self.s_out)
         self.seq += 1
 
     def wait(self):
-        for st in (self.s_in, self.s_comm, self.s_k, self.s_out):
+        for st in (self.s_in, self.s_comm, self.s_k, self.s_x, self.s_out):
             st.synchronize()
         self._keep.clear()
 
     def leg_ms(self):
-        """Device time of the four legs of the most recent call (after wait()): input copy,
-        all-gather, kernels, output copy.  Legs of consecutive calls overlap, so the step time of a
-        stream of calls tends to the longest leg, not to their sum."""
+        """Device time of the legs of the most recent call (after wait()): input copy, exchange of B,
+        kernels, re-deal of C, output copy.  Legs of consecutive calls overlap, so the step time of a
+        stream of calls tends to the longest leg, not to their sum; an exchange leg includes the
+        time it waits for the slowest peer."""
         if self.seq == 0:
-            return {"h2d_ms": 0.0, "allgather_ms": 0.0, "kernel_ms": 0.0, "d2h_ms": 0.0}
+            return {"h2d_ms": 0.0, "allgather_ms": 0.0, "kernel_ms": 0.0, "redeal_ms": 0.0, "d2h_ms": 0.0}
         s = (self.seq - 1) & 1
         return {"h2d_ms": self.in_start[s].elapsed_time(self.in_done[s]),
                 "allgather_ms": self.comm_start[s].elapsed_time(self.comm_done[s]),
                 "kernel_ms": self.k_start[s].elapsed_time(self.k_done[s]),
+                "redeal_ms": self.x_start[s].elapsed_time(self.x_done[s]) if self.row_cuts is not None else 0.0,
                 "d2h_ms": self.out_start[s].elapsed_time(self.out_done[s])}
