@@ -332,49 +332,10 @@ def run_ours(args, rank, world, local_rank):
                         "window_column_pairs_after": R.window_column_pairs(rp, col)}
         del rid
     if world > 1:
-        # first cut by nnz; then re-cut by the k-steps the built format really has per window
-        # (hub windows share columns, so their cost per nnz is lower) and build again
-        (r0, r1), (rp_l, col_l, val_l) = shard.shard_for_rank(rp, col, val, rank, world)
-        fmt, st = build_format(rp_l, col_l, val_l, strict=args.strict)
-        W = (n + 15) // 16
-        cost = torch.zeros(W, device=dev)
-        w0 = r0 // 16
-        mine = shard.window_steps(fmt, (r1 - r0 + 15) // 16) + 6.0   # + fixed per-window overhead
-        cost[w0:w0 + mine.numel()] = mine
-        dist.all_reduce(cost, op=dist.ReduceOp.SUM)
-        cuts = shard.cuts_from_window_costs(cost, world, n)
+        # cut by nnz, re-cut by the k-steps of the built format, then by measured kernel time
+        cuts = shard.refined_cuts(rp, col, val, rank, world, F, strict=args.strict)
         r0, r1 = cuts[rank], cuts[rank + 1]
         rp_l, col_l, val_l = shard.slice_csr(rp, col, val, r0, r1)
-        del fmt
-        # up to two refinements by measured kernel time (hub windows and L2 behaviour are not in the
-        # step count): time the rank's own kernel, make the slow ranks' windows heavier, cut again
-        Bt = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
-        for _ in range(2):
-            fmt_t, _st = build_format(rp_l, col_l, val_l, strict=args.strict)
-            plan_t = SpmmPlan(fmt_t, max(r1 - r0, 1), n, validate=False)
-            out_t = torch.empty((max(r1 - r0, 1), F), dtype=torch.float16, device=dev)
-            for _i in range(3):
-                plan_t.run(Bt, out=out_t)
-            torch.cuda.synchronize()
-            dist.barrier()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _i in range(5):
-                plan_t.run(Bt, out=out_t)
-            a1.record()
-            torch.cuda.synchronize()
-            mine_t = torch.tensor([a0.elapsed_time(a1) / 5], device=dev)
-            all_t = [torch.zeros_like(mine_t) for _i in range(world)]
-            dist.all_gather(all_t, mine_t)
-            times = [float(t) for t in all_t]
-            del plan_t, fmt_t, out_t
-            if max(times) <= 1.03 * (sum(times) / world):
-                break
-            cost = shard.rescale_costs(cost, cuts, times)
-            cuts = shard.cuts_from_window_costs(cost, world, n)
-            r0, r1 = cuts[rank], cuts[rank + 1]
-            rp_l, col_l, val_l = shard.slice_csr(rp, col, val, r0, r1)
-        del Bt
     else:
         r0, r1, rp_l, col_l, val_l = 0, n, rp, col, val
     m_local = r1 - r0
@@ -788,7 +749,9 @@ def run_gcn(args, rank, world, local_rank):
     X = torch.randn(n, 256, device=dev, generator=g).half()
     W1 = (torch.randn(256, 128, device=dev, generator=g) * 0.02).half()
     W2 = (torch.randn(128, 64, device=dev, generator=g) * 0.02).half()
-    model = ShardedGCN2(rp, col, val, rank, world, strict=args.strict)
+    from trspmm import shard
+    cuts = shard.refined_cuts(rp, col, val, rank, world, 128, strict=args.strict) if world > 1 else None
+    model = ShardedGCN2(rp, col, val, rank, world, cuts=cuts, strict=args.strict)
     kept = model.stats["nnz"] - model.stats["dropped_nnz"]
     for _ in range(args.warmup):
         model.forward(X, W1, W2, gather=args.gather)

@@ -5,16 +5,19 @@
 //   * a packed 2:4 tile  (s_tile_column / s_packed_a / s_packed_meta, block_online.cpp:796-841)
 //     -> one mma.sp m16n8k16 per 8 features, or
 //   * a pair of dense 16x8 TC blocks (t_column / t_binary / t_value, block_online.cpp:444-540)
-//     -> one dense mma m16n8k16 per 8 features.
+//     -> one dense mma m16n8k16 per 8 features, or
+//   * 16 entries of the window's CSR remainder -> one dense mma m16n8k16 per 8 features.
 // The default kernel gives every item to ONE warp: the warp gathers the 16 B rows of a step with
-// 16-byte cp.async into its own padded shared-memory ring, feeds them to the tensor cores with
+// 16-byte cp.async into its own shared-memory ring, feeds them to the tensor cores with
 // ldmatrix.trans and keeps the fp32 accumulators of all 16 x FS outputs in registers across the
 // item.  No block-wide barrier exists anywhere in the loop; measured on B200, the barrier per
 // k-step of a CTA-cooperative gather, not the bytes in flight, was what held the gather rate at
 // 8.7 TB/s where warp-private rings reach 14 TB/s on the same column stream.
 // The CSR remainder parts of the window (c_* / cs_* arrays, block_online.cpp:397-439; kernels
-// mGCNkernel.cu:976-1042, 1119-1171) are added by the same warp with 16-byte B-row loads, one
-// entry per lane group and a shuffle reduction across the groups, and C is written exactly once:
+// mGCNkernel.cu:976-1042, 1119-1171) run through the same pipeline: the plan expands them into
+// groups of 16 entries, a group's 16 columns are gathered like a tile's and multiplied by a
+// 16 x 16 A tile holding entry k in column k (the fallback kernel for unaligned operands adds
+// them with scalar loads instead), and C is written exactly once:
 // no memset, no atomics, no second output buffer, no add kernel (compare
 // mGCNkernel_online.cu:1589-1590, 1689-1712).  Heavy windows are cut into several items that
 // write fp32 partial sums to scratch; a second kernel adds them in a fixed order, so results are
@@ -37,7 +40,7 @@ constexpr int kIdxRing = 8;                 // slots of 16 column ids; >= kIdxAh
 constexpr int kARegionBytes = 768;   // sparse: 256 B A + 32 B meta; dense: 16 rows x 48 B
 constexpr int kDenseRowHalfs = 24;   // 48-byte row stride of the expanded dense A tile
 
-struct Item {        // 48 bytes: everything a warp / CTA needs to start
+struct Item {        // 64 bytes: everything a warp / CTA needs to start
     int window;      // window id
     int step_begin;  // k-steps of the window this item covers
     int step_end;
@@ -50,6 +53,9 @@ struct Item {        // 48 bytes: everything a warp / CTA needs to start
     int c_end;
     int cs_begin;    // short CSR parts this item adds
     int cs_end;
+    int ce0;         // the same CSR entries as groups of 16 (plan-owned expansion): first group, count
+    int ce_n;
+    int pad[2];
 };
 
 struct Heavy {
@@ -65,6 +71,8 @@ struct WindowRanges {
     int* c_end;
     int* cs_begin;   // short CSR parts per window
     int* cs_end;
+    int* ce_begin;   // first group of 16 expanded CSR entries per window ([W + 1], exclusive scan of ce_count)
+    int* ce_count;
 };
 
 struct KernelArgs {
@@ -75,6 +83,8 @@ struct KernelArgs {
     void* C;
     float* scratch;
     const __half* tc_dense;        // [blocks][16][8] expanded TC blocks (plan-owned)
+    const int* ce_col;             // [groups][16] column ids of the CSR remainder entries, -1 = padding (plan-owned)
+    const unsigned* ce_rv;         // [groups][16] fp16 value | local row << 16
     int m_rows, k_cols, window, F, out_half;
     int relu;                      // 1: C = max(A'B, 0) (GCN layer epilogue)
     void* peers[8];                // fused exchange: the fp16 rows are written into every one of these
@@ -95,6 +105,41 @@ __global__ void k_part_ranges(const int* __restrict__ key, const int* __restrict
     int hi = use_prefix ? prefix[p + 1] : p + 1;
     if (p == 0 || key[p - 1] / div != w) begin[w] = lo;
     if (p == n - 1 || key[p + 1] / div != w) end[w] = hi;
+}
+
+// CSR remainder entries of a window (long parts first, then short parts), expanded at plan time
+// into groups of 16 entries - column id and (fp16 value, local row) - so that the warp kernel can
+// run them through its gather pipeline as k-steps of their own: 16 gathered B rows times a
+// 16 x 16 A tile that holds entry k in column k (one non-zero per column).
+__global__ void k_ce_count(trs_format f, WindowRanges wr, int num_windows) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w > num_windows) return;
+    int n = 0;
+    if (w < num_windows) {
+        if (wr.c_end[w] > wr.c_begin[w]) n += f.c_row_offset[wr.c_end[w]] - f.c_row_offset[wr.c_begin[w]];
+        if (wr.cs_end[w] > wr.cs_begin[w]) n += f.cs_row_offset[wr.cs_end[w]] - f.cs_row_offset[wr.cs_begin[w]];
+    }
+    wr.ce_count[w] = n > 0 ? (n + 15) / 16 : 0;
+}
+__global__ void k_ce_fill(trs_format f, WindowRanges wr, int num_windows, int window, int pass, long long capacity,
+                          int* __restrict__ ce_col, unsigned* __restrict__ ce_rv) {
+    const int n = pass ? f.parts_c_short : f.parts_c;
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n) return;
+    const int* roff = pass ? f.cs_row_offset : f.c_row_offset;
+    const int* rrow = pass ? f.cs_row : f.c_row;
+    const int* rcol = pass ? f.cs_column : f.c_column;
+    const __half* rval = (const __half*)(pass ? f.cs_value : f.c_value);
+    const int w = rrow[p] / window;
+    if (w < 0 || w >= num_windows) return;  // reported by validation
+    const int lr = rrow[p] - w * window;
+    long long dst = (long long)wr.ce_begin[w] * 16 + (roff[p] - (pass ? f.cs_row_offset[wr.cs_begin[w]] : f.c_row_offset[wr.c_begin[w]]));
+    if (pass && wr.c_end[w] > wr.c_begin[w]) dst += f.c_row_offset[wr.c_end[w]] - f.c_row_offset[wr.c_begin[w]];
+    for (int e = roff[p]; e < roff[p + 1]; ++e, ++dst) {
+        if (dst < 0 || dst >= capacity) return;
+        ce_col[dst] = rcol[e];
+        ce_rv[dst] = (unsigned)__half_as_ushort(rval[e]) | ((unsigned)lr << 16);
+    }
 }
 
 __global__ void k_count_items(trs_format f, WindowRanges wr, int num_windows, int chunk, int* __restrict__ n_items,
@@ -124,8 +169,9 @@ __global__ void k_fill_items(trs_format f, WindowRanges wr, int num_windows, int
     const int tile0 = (w < f.num_windows) ? f.s_window_tile_offset[w] : 0;
     const int blk0 = wr.blk_begin[w], blk_end = wr.blk_end[w];
     const int cb = wr.c_begin[w], cn = wr.c_end[w] - cb, sb = wr.cs_begin[w], sn = wr.cs_end[w] - sb;
+    const int g0 = wr.ce_begin[w], gn = wr.ce_count[w];
     if (n == 1) {
-        items[item_off[w]] = Item{w, 0, steps, -1, tile0, tiles, blk0, blk_end, cb, cb + cn, sb, sb + sn};
+        items[item_off[w]] = Item{w, 0, steps, -1, tile0, tiles, blk0, blk_end, cb, cb + cn, sb, sb + sn, g0, gn, {0, 0}};
         return;
     }
     // split evenly so that no item is much shorter than the others; the window's CSR parts are
@@ -135,7 +181,9 @@ __global__ void k_fill_items(trs_format f, WindowRanges wr, int num_windows, int
         int b = min(i * per, steps), e = min(b + per, steps);
         items[item_off[w] + i] = Item{w, b, e, slot_off[w] + i, tile0, tiles, blk0, blk_end,
                                       cb + (int)((long long)cn * i / n), cb + (int)((long long)cn * (i + 1) / n),
-                                      sb + (int)((long long)sn * i / n), sb + (int)((long long)sn * (i + 1) / n)};
+                                      sb + (int)((long long)sn * i / n), sb + (int)((long long)sn * (i + 1) / n),
+                                      g0 + (int)((long long)gn * i / n),
+                                      (int)((long long)gn * (i + 1) / n) - (int)((long long)gn * i / n), {0, 0}};
     }
     heavy[heavy_off[w]] = Heavy{w, slot_off[w], slot_off[w] + n};
 }
@@ -161,7 +209,7 @@ __global__ void k_check_range(const int* __restrict__ a, long long n, int lo, in
 __global__ void k_item_class(const Item* __restrict__ items, int n, unsigned char* __restrict__ cls) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const int steps = items[i].step_end - items[i].step_begin;
+    const int steps = items[i].step_end - items[i].step_begin + items[i].ce_n;
     cls[i] = steps >= 192 ? 0 : steps >= 96 ? 1 : steps >= 48 ? 2 : 3;
 }
 
@@ -461,92 +509,6 @@ struct WarpTile {
     __device__ static constexpr int swz(int r) { return FS == 32 ? ((r >> 1) & 3) : (r & 7); }
 };
 
-// Adds the item's CSR remainder parts into a zeroed 16 x FS fp32 tile in shared memory.  A group
-// of FS / 8 lanes reads one B row segment with 16-byte loads; the 32 / (FS / 8) groups of the warp
-// take different entries of the part and their partial sums meet in a shuffle reduction.  The
-// part headers (row, entry range) are read 32 parts at a time and the column ids and values 32
-// entries at a time, one per lane, and handed round with shuffles, so that the only dependent
-// loads left in the loop are the B-row gathers themselves, four of them in flight per lane.
-template <int FS>
-__device__ __forceinline__ void csr_parts_to_tile(const Item& it, const KernelArgs& a, int fbase, int lane, float* tile) {
-    constexpr int LPR = FS / 8, G = 32 / LPR, PITCH = FS + 4;  // floats
-    constexpr int U = 4;                                       // B-row loads in flight per lane
-    const int grp = lane / LPR, ch = lane % LPR;
-    const bool fin = fbase + ch * 8 < a.F;
-    const uint4* Bq = (const uint4*)a.B;
-    const uint32_t pitch16 = (uint32_t)a.F >> 3;
-    const uint32_t chunk16 = ((uint32_t)fbase >> 3) + ch;
-    for (int pass = 0; pass < 2; ++pass) {
-        const int pb = pass ? it.cs_begin : it.c_begin;
-        const int pe = pass ? it.cs_end : it.c_end;
-        const int* roff = pass ? a.f.cs_row_offset : a.f.c_row_offset;
-        const int* rrow = pass ? a.f.cs_row : a.f.c_row;
-        const int* rcol = pass ? a.f.cs_column : a.f.c_column;
-        const __half* rval = (const __half*)(pass ? a.f.cs_value : a.f.c_value);
-        for (int p0 = pb; p0 < pe; p0 += 32) {
-            const int np = min(32, pe - p0);
-            int h_row = 0, h_e0 = 0, h_e1 = 0;
-            if (lane < np) {
-                h_row = __ldg(rrow + p0 + lane) - it.window * a.window;
-                h_e0 = __ldg(roff + p0 + lane);
-                h_e1 = __ldg(roff + p0 + lane + 1);
-            }
-            for (int pi = 0; pi < np; ++pi) {
-                const int lr = __shfl_sync(0xffffffffu, h_row, pi);
-                const int e0 = __shfl_sync(0xffffffffu, h_e0, pi);
-                const int e1 = __shfl_sync(0xffffffffu, h_e1, pi);
-                float s[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) s[i] = 0.f;
-                for (int eb = e0; eb < e1; eb += 32) {
-                    const int cnt = min(32, e1 - eb);
-                    int my_c = 0;
-                    float my_v = 0.f;
-                    if (lane < cnt) {
-                        my_c = __ldg(rcol + eb + lane);
-                        my_v = __half2float(__ldg(rval + eb + lane));
-                    }
-                    for (int i0 = 0; i0 < cnt; i0 += G * U) {
-                        uint4 q[U];
-                        float v[U];
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const int idx = i0 + grp + G * u;
-                            const int c = __shfl_sync(0xffffffffu, my_c, idx & 31);
-                            v[u] = __shfl_sync(0xffffffffu, my_v, idx & 31);
-                            q[u] = make_uint4(0u, 0u, 0u, 0u);
-                            if (idx < cnt && fin) q[u] = __ldg(Bq + (size_t)((uint32_t)c * pitch16 + chunk16));
-                            else v[u] = 0.f;
-                        }
-#pragma unroll
-                        for (int u = 0; u < U; ++u) {
-                            const __half2* h = (const __half2*)&q[u];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float2 x = __half22float2(h[i]);
-                                s[2 * i] = fmaf(v[u], x.x, s[2 * i]);
-                                s[2 * i + 1] = fmaf(v[u], x.y, s[2 * i + 1]);
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int off = LPR; off < 32; off <<= 1)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], off);
-                if (grp == 0 && lr >= 0 && lr < 16) {
-                    float4* d = (float4*)(tile + lr * PITCH + ch * 8);
-                    float4 u = d[0], w = d[1];
-                    u.x += s[0]; u.y += s[1]; u.z += s[2]; u.w += s[3];
-                    w.x += s[4]; w.y += s[5]; w.z += s[6]; w.w += s[7];
-                    d[0] = u; d[1] = w;
-                }
-                __syncwarp();
-            }
-        }
-    }
-}
-
 // Epilogue of a warp-owned item.  Accumulators are in mma fragment layout: acc[n][2h + i] = row
 // g + 8h, feature fbase + 8n + 2t + i.  The result tile is staged in the warp's (drained) ring and
 // leaves in 16-byte pieces of whole rows: fp32 partial sums to a scratch slot, or fp16 / fp32
@@ -556,22 +518,6 @@ __device__ __forceinline__ void finish_item_warp(float (&acc)[FS / 8][4], const 
                                                  int lane, unsigned char* ring) {
     constexpr int NT = FS / 8;
     const int g = lane >> 2, t = lane & 3;
-    if (it.c_end > it.c_begin || it.cs_end > it.cs_begin) {
-        constexpr int PITCH = FS + 4;
-        float* tile = (float*)ring;
-        for (int i = lane; i < 16 * PITCH / 4; i += 32) ((float4*)tile)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        __syncwarp();
-        csr_parts_to_tile<FS>(it, a, fbase, lane, tile);
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float2 x = *(const float2*)(tile + (g + 8 * h) * PITCH + 8 * n + 2 * t);
-                acc[n][2 * h] += x.x;
-                acc[n][2 * h + 1] += x.y;
-            }
-        __syncwarp();
-    }
     const bool partial = it.slot >= 0;
     if (a.relu && !partial) {
 #pragma unroll
@@ -635,8 +581,9 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
     const int fbase = blockIdx.y * FS;
 
     const Item it = a.items[blockIdx.x];
-    const int nsteps = it.step_end - it.step_begin;
-    const int nsparse = min(max(it.ntiles - it.step_begin, 0), nsteps);  // steps [0, nsparse) are packed tiles
+    const int nmain = it.step_end - it.step_begin;
+    const int nsparse = min(max(it.ntiles - it.step_begin, 0), nmain);   // steps [0, nsparse) are packed tiles,
+    const int nsteps = nmain + it.ce_n;                                  // [nsparse, nmain) TC pairs, the rest CSR groups
 
     const uint32_t smem0 = smem_u32(smem);
     const uint32_t ring0 = smem0 + T::STAGE * STAGES;
@@ -666,7 +613,9 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
         if (lane < 4 && m < nsteps) {
             const int s = it.step_begin + m;
             const uint32_t dst = ring0 + (m & (T::RING - 1)) * 64 + lane * 16;
-            if (s < it.ntiles) {
+            if (m >= nmain) {
+                cp_async16(dst, a.ce_col + (size_t)(it.ce0 + m - nmain) * 16 + lane * 4, 16);
+            } else if (s < it.ntiles) {
                 cp_async16(dst, a.f.s_tile_column + (size_t)(it.tile0 + s) * 16 + lane * 4, 16);
             } else {
                 const int b = it.blk0 + 2 * (s - it.ntiles) + (lane >> 1);
@@ -705,7 +654,11 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
         uint4 r = make_uint4(0u, 0u, 0u, 0u);
         if (j >= nsteps) return r;
         const int s = it.step_begin + j;
-        if (s < it.ntiles) {
+        if (j >= nmain) {  // entries 2t, 2t+1, 2t+8, 2t+9 of the group, as stored (value | row << 16)
+            const unsigned* rv = a.ce_rv + (size_t)(it.ce0 + j - nmain) * 16 + 2 * t;
+            const uint2 lo = __ldg((const uint2*)rv), hi = __ldg((const uint2*)(rv + 8));
+            r = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        } else if (s < it.ntiles) {
             const size_t tile = (size_t)(it.tile0 + s);
             const uint2 v = __ldg((const uint2*)(a.f.s_packed_a + tile * 64) + lane);
             r.x = v.x; r.y = v.y;
@@ -734,12 +687,23 @@ __global__ void __launch_bounds__(32, MINB) k_window_spmm_warp(const KernelArgs 
                 mma_sp_16816(acc[2 * h + 1], av.x, av.y, b2, b3, av.z);
             }
         } else {
+            uint32_t a0 = av.x, a1 = av.y, a2 = av.z, a3 = av.w;
+            if (j >= nmain) {
+                // CSR group: A[r][k] = value of entry k if its row is r.  Fragment words: rows g / g + 8,
+                // columns (2t, 2t+1) and (2t+8, 2t+9)
+                auto pick = [](uint32_t e, uint32_t row) -> uint32_t { return (e >> 16) == row ? (e & 0xffffu) : 0u; };
+                const uint32_t rlo = (uint32_t)g, rhi = (uint32_t)g + 8u;
+                a0 = pick(av.x, rlo) | (pick(av.y, rlo) << 16);
+                a1 = pick(av.x, rhi) | (pick(av.y, rhi) << 16);
+                a2 = pick(av.z, rlo) | (pick(av.w, rlo) << 16);
+                a3 = pick(av.z, rhi) | (pick(av.w, rhi) << 16);
+            }
 #pragma unroll
             for (int h = 0; h < T::NT / 2; ++h) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(baddr + (((2 * h + lchunk) ^ lswz) << 4), b0, b1, b2, b3);
-                mma_16816(acc[2 * h], av.x, av.y, av.z, av.w, b0, b1);
-                mma_16816(acc[2 * h + 1], av.x, av.y, av.z, av.w, b2, b3);
+                mma_16816(acc[2 * h], a0, a1, a2, a3, b0, b1);
+                mma_16816(acc[2 * h + 1], a0, a1, a2, a3, b2, b3);
             }
         }
     };
@@ -840,6 +804,8 @@ struct trs_spmm_plan {
     DevBuf<Item> items_sorted;        // the same items, long ones first (whole-matrix runs)
     DevBuf<Heavy> heavy;
     DevBuf<__half> tc_dense;          // TC blocks expanded to dense 16 x 8 fp16 tiles
+    DevBuf<int> ce_col;               // CSR remainder entries in groups of 16: column ids (-1 = padding)
+    DevBuf<unsigned> ce_rv;           //   and fp16 value | local row << 16
     int n_items, n_heavy, n_slots;
     std::vector<int> h_item_off, h_heavy_off;  // host copies of the per-window prefixes (num_windows + 1 each)
     bool arrays_aligned;              // index / tile arrays are 16-byte aligned
@@ -948,10 +914,11 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     DevBuf<int> ranges, cnt, off;
     DevBuf<unsigned char> tmp;
     auto fail = [&](int code) { ranges.release(); cnt.release(); off.release(); tmp.release(); trs_spmm_plan_destroy(p); return code; };
-    int rc = ranges.alloc((size_t)6 * W);
+    int rc = ranges.alloc((size_t)6 * W + 2 * ((size_t)W + 1));
     if (rc) return fail(rc);
-    cudaMemsetAsync(ranges.p, 0, sizeof(int) * 6 * W, st);
-    WindowRanges wr{ranges.p, ranges.p + W, ranges.p + 2 * W, ranges.p + 3 * W, ranges.p + 4 * W, ranges.p + 5 * W};
+    cudaMemsetAsync(ranges.p, 0, sizeof(int) * ((size_t)6 * W + 2 * ((size_t)W + 1)), st);
+    WindowRanges wr{ranges.p, ranges.p + W, ranges.p + 2 * W, ranges.p + 3 * W, ranges.p + 4 * W, ranges.p + 5 * W,
+                    ranges.p + (size_t)6 * W, ranges.p + (size_t)6 * W + (W + 1)};
     auto grid = [](long long n) { return (unsigned)((n + 255) / 256); };
     if (f.parts_t > 0)
         k_part_ranges<<<grid(f.parts_t), 256, 0, st>>>(f.t_window_row, f.t_row_offset, f.parts_t, 16, W,
@@ -969,6 +936,28 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     if (!rc) rc = tmp.alloc(tmp_bytes + 16);
     if (rc) return fail(rc);
     cudaMemsetAsync(cnt.p, 0, sizeof(int) * 3 * (W + 1), st);
+    // CSR remainder entries, expanded into groups of 16 per window
+    {
+        k_ce_count<<<grid(W + 1), 256, 0, st>>>(f, wr, W);
+        cub::DeviceScan::ExclusiveSum(tmp.p, tmp_bytes, wr.ce_count, wr.ce_begin, W + 1, st);
+        int groups = 0;
+        cudaError_t ee = cudaMemcpyAsync(&groups, wr.ce_begin + W, sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (ee == cudaSuccess) ee = cudaStreamSynchronize(st);
+        if (ee != cudaSuccess) return fail((int)ee);
+        if (groups < 0) return fail(TRS_E_OFFSETS);
+        const size_t cap = (size_t)groups * 16;
+        rc = p->ce_col.alloc(cap);
+        if (!rc) rc = p->ce_rv.alloc(cap);
+        if (rc) return fail(rc);
+        if (cap > 0) {
+            cudaMemsetAsync(p->ce_col.p, 0xff, cap * sizeof(int), st);
+            cudaMemsetAsync(p->ce_rv.p, 0, cap * sizeof(unsigned), st);
+            if (f.parts_c > 0)
+                k_ce_fill<<<grid(f.parts_c), 256, 0, st>>>(f, wr, W, window, 0, (long long)cap, p->ce_col.p, p->ce_rv.p);
+            if (f.parts_c_short > 0)
+                k_ce_fill<<<grid(f.parts_c_short), 256, 0, st>>>(f, wr, W, window, 1, (long long)cap, p->ce_col.p, p->ce_rv.p);
+        }
+    }
     k_count_items<<<grid(W), 256, 0, st>>>(f, wr, W, p->chunk, cnt.p, cnt.p + (W + 1), cnt.p + 2 * (W + 1));
     for (int i = 0; i < 3; ++i)
         cub::DeviceScan::ExclusiveSum(tmp.p, tmp_bytes, cnt.p + (size_t)i * (W + 1), off.p + (size_t)i * (W + 1), W + 1, st);
@@ -1039,6 +1028,8 @@ extern "C" int trs_spmm_plan_destroy(trs_spmm_plan* p) {
     p->items_sorted.release();
     p->heavy.release();
     p->tc_dense.release();
+    p->ce_col.release();
+    p->ce_rv.release();
     delete p;
     return TRS_OK;
 }
@@ -1140,6 +1131,7 @@ static int run_impl(const trs_spmm_plan* p, const trs_half* B, void* C, int F, i
     a.n_peers = n_peers; a.peer_row0 = peer_row0;
     for (int d = 0; d < 8; ++d) a.peers[d] = d < n_peers ? peers[d] : nullptr;
     a.tc_dense = p->tc_dense.p;
+    a.ce_col = p->ce_col.p; a.ce_rv = p->ce_rv.p;
     // The warp-owner kernel moves everything in 16-byte pieces; anything else takes the fallback.
     const bool aligned = p->arrays_aligned && (F % 8 == 0) &&
                          ((((uintptr_t)B | (uintptr_t)C | (uintptr_t)workspace) & 15) == 0);
