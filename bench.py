@@ -146,7 +146,7 @@ def make_matrix(workload, device):
 # DRAM bytes of one launch of the window kernel on one GPU (dram__bytes_read.sum +
 # dram__bytes_write.sum of single-metric, one-pass ncu captures of this very command; the
 # summaries under profiles/ give the commands).  Workloads not captured report null.
-MEASURED_TRAFFIC = {("rmat21", 128): 8.177e9 + 0.616e9, ("rmat20", 128): 1.664e9 + 0.2575e9}
+MEASURED_TRAFFIC = {("rmat21", 128): 8.090e9 + 0.616e9, ("rmat20", 128): 1.647e9 + 0.2582e9}
 
 
 def algorithmic_bytes(nnz, n_rows, n_cols, F, out_bytes):

@@ -275,15 +275,17 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
     const uint4* Xq = (const uint4*)X + t;
     const uint4* Yq = (const uint4*)Y;
 
-    auto issue_rec = [&](int j) {   // record of block j -> record ring (8 lanes x 16 B)
-        if (j < nb && lane < 8) cp_async16(recs0 + (j & (kRecRing - 1)) * 128 + lane * 16, (const uint4*)(blk + b0 + j) + lane, 16);
+    // `slot` / `stage` arguments are the ring positions of block j, passed separately so that they are
+    // compile-time constants inside the unrolled loop below
+    auto issue_rec = [&](int j, int slot) {   // record of block j -> record ring (8 lanes x 16 B)
+        if (j < nb && lane < 8) cp_async16(recs0 + slot * 128 + lane * 16, (const uint4*)(blk + b0 + j) + lane, 16);
     };
     // Y rows of block j (its record is in the ring): lane copies chunks (lane & 3) + 4 i of row lane >> 2
-    auto issue_rows = [&](int j) {
+    auto issue_rows = [&](int j, int slot, int stage) {
         if (j >= nb) return;
-        const int c = *(const int*)(recs + (j & (kRecRing - 1)) * 128 + g * 4);
+        const int c = *(const int*)(recs + slot * 128 + g * 4);
         const uint4* src = Yq + (size_t)max(c, 0) * ROW16;
-        const uint32_t dst = rows0 + (j % kRowStages) * R::STAGE + g * R::ROWB;
+        const uint32_t dst = rows0 + stage * R::STAGE + g * R::ROWB;
 #pragma unroll
         for (int i = 0; i < KCH; ++i) {
             const int chunk = t + 4 * i;
@@ -294,14 +296,14 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
     // holding the rows of block j + kRowAhead and the record of block j + kRecAhead; the rows of
     // blocks 0 .. kRowAhead-1 are kRowAhead groups of their own.  At iteration j all but the newest
     // kRowAhead-1 groups are complete: the rows of block j and the record of block j + kRowAhead.
-#pragma unroll 1
-    for (int j = 0; j < kRecAhead; ++j) issue_rec(j);
+#pragma unroll
+    for (int j = 0; j < kRecAhead; ++j) issue_rec(j, j);
     cp_async_commit();
     cp_async_wait<0>();
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < kRowAhead; ++j) {
-        issue_rows(j);
+        issue_rows(j, j, j);
         cp_async_commit();
     }
 
@@ -309,43 +311,49 @@ __global__ void __launch_bounds__(128, MINB) k_sddmm_tc_ring(const SddmmBlock* _
     uint4 xa[KCH], xb[KCH];
 #pragma unroll
     for (int c = 0; c < KCH; ++c) xa[c] = xb[c] = make_uint4(0, 0, 0, 0);
-    for (int j = 0; j < nb; ++j) {
-        cp_async_wait<kRowAhead - 1>();
-        __syncwarp();
-        issue_rec(j + kRecAhead);
-        issue_rows(j + kRowAhead);
-        cp_async_commit();
-        const unsigned char* rec = recs + (j & (kRecRing - 1)) * 128;
-        const int w = *(const int*)(rec + 48);
-        const unsigned wa = *(const unsigned*)(rec + 32 + (g >> 2) * 4), wb = *(const unsigned*)(rec + 32 + ((g >> 2) + 2) * 4);
-        if (w != cur_w) {  // warp-uniform
-            cur_w = w;
-            const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
+    static_assert(kRecRing == 8 && kRowStages == 4, "the loop is unrolled by the record ring");
+    for (int j0 = 0; j0 < nb; j0 += kRecRing) {
+#pragma unroll
+        for (int u = 0; u < kRecRing; ++u) {
+            const int j = j0 + u;
+            if (j >= nb) break;
+            cp_async_wait<kRowAhead - 1>();
+            __syncwarp();
+            issue_rec(j + kRecAhead, (u + kRecAhead) & (kRecRing - 1));
+            issue_rows(j + kRowAhead, (u + kRowAhead) & (kRecRing - 1), (u + kRowAhead) & (kRowStages - 1));
+            cp_async_commit();
+            const unsigned char* rec = recs + u * 128;
+            const int w = *(const int*)(rec + 48);
+            const unsigned wa = *(const unsigned*)(rec + 32 + (g >> 2) * 4), wb = *(const unsigned*)(rec + 32 + ((g >> 2) + 2) * 4);
+            if (w != cur_w) {  // warp-uniform
+                cur_w = w;
+                const int ra = min(w * 16 + g, n_rows - 1), rb = min(w * 16 + g + 8, n_rows - 1);
+#pragma unroll
+                for (int ch = 0; ch < KCH; ++ch) {
+                    xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
+                    xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
+                }
+            }
+            const unsigned char* yrow = rows + (u & (kRowStages - 1)) * R::STAGE + g * R::ROWB;
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < KCH; ++ch) {
-                xa[ch] = __ldg(Xq + (size_t)ra * ROW16 + ch * 4);
-                xb[ch] = __ldg(Xq + (size_t)rb * ROW16 + ch * 4);
+                const uint4 y = *(const uint4*)(yrow + (((4 * ch + t) ^ ((g & 1) << 2)) & (R::CPR - 1)) * 16);
+                mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y.x, y.y);
+                mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y.z, y.w);
             }
-        }
-        const unsigned char* yrow = rows + (j % kRowStages) * R::STAGE + g * R::ROWB;
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < KCH; ++ch) {
-            const uint4 y = *(const uint4*)(yrow + (((4 * ch + t) ^ ((g & 1) << 2)) & (R::CPR - 1)) * 16);
-            mma_16816(d, xa[ch].x, xb[ch].x, xa[ch].y, xb[ch].y, y.x, y.y);
-            mma_16816(d, xa[ch].z, xb[ch].z, xa[ch].w, xb[ch].w, y.z, y.w);
-        }
-        const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
-        const int n0 = 2 * t;
-        if ((ba >> n0) & 3u) {
-            const int s = *(const int*)(rec + 64 + g * 4) + __popc(ba & ((1u << n0) - 1u));
-            if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
-            if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
-        }
-        if ((bbits >> n0) & 3u) {
-            const int s = *(const int*)(rec + 64 + (g + 8) * 4) + __popc(bbits & ((1u << n0) - 1u));
-            if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
-            if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
+            const unsigned ba = (wa >> ((g & 3) << 3)) & 0xffu, bbits = (wb >> ((g & 3) << 3)) & 0xffu;
+            const int n0 = 2 * t;
+            if ((ba >> n0) & 3u) {
+                const int s = *(const int*)(rec + 64 + g * 4) + __popc(ba & ((1u << n0) - 1u));
+                if ((ba >> n0) & 1u) out[s] = __float2half_rn(d[0]);
+                if ((ba >> n0) & 2u) out[s + ((ba >> n0) & 1u)] = __float2half_rn(d[1]);
+            }
+            if ((bbits >> n0) & 3u) {
+                const int s = *(const int*)(rec + 64 + (g + 8) * 4) + __popc(bbits & ((1u << n0) - 1u));
+                if ((bbits >> n0) & 1u) out[s] = __float2half_rn(d[2]);
+                if ((bbits >> n0) & 2u) out[s + ((bbits >> n0) & 1u)] = __float2half_rn(d[3]);
+            }
         }
     }
     cp_async_wait<0>();
