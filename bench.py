@@ -692,8 +692,9 @@ def run_build(args):
 
 
 def run_match24(args):
-    """2:4 matching statistics (the reference's match_2to4* modules): the three deterministic variants on the GPU,
-    the reference's compiled CPU modules timed beside them on a bounded sample."""
+    """2:4 matching statistics (the reference's match_2to4* modules) on the GPU: the three variants with a
+    CPU reference (its compiled modules timed beside them on a bounded sample) and the two restated
+    from the reference's GPU matchers (online, cuda: no CPU module exists for those)."""
     from trspmm import match24
     dev = torch.device("cuda", 0)
     rp, col, val, _ = make_matrix(args.workload, dev)
@@ -702,7 +703,7 @@ def run_match24(args):
     ref_names = {"para_dr": ("matching_utils", "match_2to4"), "hash": ("matching_utils_hash", "match_2to4_hash"),
                  "bucket": ("matching_utils_bucket", "match_2to4_bucket")}
     out = {}
-    for variant in ("para_dr", "hash", "bucket"):
+    for variant in ("para_dr", "hash", "bucket", "online", "cuda"):
         for _ in range(args.warmup):
             match24.match_stats(variant, rp, col)
         torch.cuda.synchronize()
@@ -713,7 +714,7 @@ def run_match24(args):
         alg = nnz * 4 + (n + 1) * 4
         out[variant] = {"ms": ms, "Mnnz_per_s": nnz / (ms * 1e-3) / 1e6, "GBps": alg / (ms * 1e-3) / 1e9,
                         "frac": alg / (ms * 1e-3) / 1e9 / peak}
-        if not args.no_cpu:
+        if not args.no_cpu and variant in ref_names:
             from oracle import oracle as O
             mod = O.reference_module(ref_names[variant][0])
             if mod is not None:
@@ -841,7 +842,7 @@ def main():
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "push"],
                     help="multi-GPU host-buffer path: how the ranks exchange their slices of B")
-    ap.add_argument("--gather", default="push", choices=["h1", "z2", "fused", "push"], help="gcn: which matrix the ranks exchange")
+    ap.add_argument("--gather", default="push", choices=["h1", "z2", "fused", "push", "gemm_bcast"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -119,8 +119,17 @@ int trs_spmm_run_ex(const trs_spmm_plan* plan, const trs_half* B, void* C, int F
 int trs_spmm_run_bcast(const trs_spmm_plan* plan, const trs_half* B, void* const* dst, int n_dst,
                        long long row0, int F, int flags, void* workspace, size_t workspace_bytes,
                        void* stream);
-/* Health word of the plan's kernels: 0, or non-zero when a bounded pipeline wait inside a kernel
- * gave up (the affected call's output is then incomplete).  Synchronises the device. */
+/* Dense row-block product fused with the exchange that follows it in a row-sharded GCN layer (no
+ * counterpart in the reference): Z[row0 + r, :] = H[r, :] * W for this GPU's `rows` rows of the
+ * hidden matrix (H: [rows, K] fp16, W: [K, N] fp16 row-major, fp32 accumulate), the fp16 rows of Z
+ * written by the same kernel into n_dst (<= 8) buffers of shape [N_total, N]: this GPU's copy and
+ * its NVLink peers' (peer-mapped pointers), 16-byte stores of whole rows.  K a multiple of 16 up
+ * to 256, N in {32, 64, 128}, N <= K, all pointers 16-byte aligned.  Asynchronous on `stream`. */
+int trs_rows_gemm_bcast(const trs_half* H, const trs_half* W, void* const* dst, int n_dst, long long row0,
+                        int rows, int K, int N, void* stream);
+/* Health word of the plan's kernels.  No kernel of the library waits on a flag or barrier another
+ * warp or kernel sets, so there is no wait that could give up: always 0.  Kept for callers of
+ * earlier versions. */
 int trs_spmm_status(const trs_spmm_plan* plan, int* status);
 /* trs_spmm_run for callers that can neither allocate device memory nor be handed any: hosts that
  * gave the whole device to their own memory pool at start-up, and latency-critical loops where

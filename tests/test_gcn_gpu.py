@@ -27,7 +27,7 @@ def _reference(rp, col, val, X, W1, W2):
     return torch.sparse.mm(A, z2)
 
 
-@pytest.mark.parametrize("gather", ["h1", "z2"])
+@pytest.mark.parametrize("gather", ["h1", "z2", "gemm_bcast"])
 def test_gcn2_single_rank(gather):
     rp, col, val = graphs.rmat_graph(12, 16, seed=4)
     n = rp.numel() - 1
@@ -56,3 +56,27 @@ def test_gcn2_two_ranks_match_single_rank():
                        timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "GCN2 ranks agree" in r.stdout
+
+
+@pytest.mark.parametrize("rows,K,N", [(1000, 128, 64), (16, 16, 32), (4099, 256, 128), (33, 64, 64)])
+def test_rows_gemm_bcast_matches_a_dense_product(rows, K, N):
+    """trs_rows_gemm_bcast with two destination buffers on one GPU: both get H @ W at the row offset,
+    nothing else is touched."""
+    from trspmm.gcn import rows_gemm_bcast
+    g = torch.Generator().manual_seed(rows)
+    H = torch.randn(rows, K, generator=g).half().cuda()
+    W = (torch.randn(K, N, generator=g) * 0.1).half().cuda()
+    row0, total = 7, rows + 20
+    dsts = [torch.full((total, N), 3.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+    rows_gemm_bcast(H, W, [d.data_ptr() for d in dsts], row0)
+    torch.cuda.synchronize()
+    ref = (H.float() @ W.float())
+    for d in dsts:
+        got = d[row0:row0 + rows].float()
+        assert torch.allclose(got, ref, rtol=2e-3, atol=2e-3), float((got - ref).abs().max())
+        assert bool((d[:row0] == 3.0).all()) and bool((d[row0 + rows:] == 3.0).all())
+    assert torch.equal(dsts[0], dsts[1])
+    with pytest.raises(Exception):
+        rows_gemm_bcast(H, W, [], 0)
+    with pytest.raises(Exception):
+        rows_gemm_bcast(H[:, :K - 8].contiguous(), W[:K - 8].contiguous(), [dsts[0].data_ptr()], 0)

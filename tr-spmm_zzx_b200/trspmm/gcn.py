@@ -17,6 +17,25 @@ from .builder import build_format
 from .spmm import SpmmPlan
 
 
+def rows_gemm_bcast(H: torch.Tensor, W: torch.Tensor, dst_ptrs, row0: int):
+    """trs_rows_gemm_bcast: Z[row0 + r] = H[r] @ W, the fp16 rows written by the one kernel into every
+    buffer of `dst_ptrs` (device pointers of [N_total, N] fp16 matrices: this GPU's and its NVLink
+    peers').  Asynchronous on the current stream."""
+    import ctypes as C
+    from . import _lib
+    if H.dtype != torch.float16 or W.dtype != torch.float16 or not H.is_cuda or H.device != W.device:
+        raise ValueError("H and W must be fp16 CUDA tensors on one device")
+    if H.dim() != 2 or W.dim() != 2 or H.shape[1] != W.shape[0] or not H.is_contiguous() or not W.is_contiguous():
+        raise ValueError("H [rows, K] and W [K, N], both contiguous")
+    if not 1 <= len(dst_ptrs) <= 8 or row0 < 0:
+        raise ValueError("1 to 8 destination buffers and a non-negative row offset")
+    lib = _lib.load()
+    arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    with torch.cuda.device(H.device):
+        _lib.check(lib.trs_rows_gemm_bcast(H.data_ptr(), W.data_ptr(), arr, len(dst_ptrs), int(row0), H.shape[0],
+                                           H.shape[1], W.shape[1], _lib.current_stream_ptr(H.device)))
+
+
 class ShardedGCN2:
     def __init__(self, rowptr, col, val, rank: int = 0, world: int = 1, window: int = 16, cuts=None, group=None,
                  strict: bool = False):
@@ -74,7 +93,8 @@ class ShardedGCN2:
         gather="fused" lets the layer-1 SpMM store its rows into every rank's H1 itself
         (peer-mapped symmetric memory, trs_spmm_run_bcast); gather="push" multiplies the own rows by W2 in
         window chunks and has the copy engines push each finished chunk into the peers' Z2 while the
-        next chunk is computed."""
+        next chunk is computed; gather="gemm_bcast" multiplies the own rows by W2 and stores the product
+        into every rank's Z2 in one kernel (trs_rows_gemm_bcast: no library GEMM, no collective)."""
         self.gather_bytes = 0
         r0, r1 = self.r0, self.r1
         marks = []
@@ -167,8 +187,25 @@ class ShardedGCN2:
                 mark("spmm1+gemm2+push")
                 hdl.barrier(channel=1)                 # all rows of all ranks have landed
                 mark("barrier")
+        elif gather == "gemm_bcast":
+            if self.world == 1:
+                h1_local = self.plan.run(z1, relu=True)
+                z2 = torch.empty((self.n, W2.shape[1]), dtype=torch.float16, device=X.device)
+                rows_gemm_bcast(h1_local[: r1 - r0].contiguous(), W2.contiguous(), [z2.data_ptr()], r0)
+                mark("spmm1+gemm2")
+            else:
+                z2, hdl = self._symmetric(W2.shape[1], X.device)
+                hdl.barrier(channel=0)                 # every rank is done reading the previous Z2
+                if r1 > r0:
+                    h1_local = self.plan.run(z1, relu=True)
+                    mark("spmm1")
+                    rows_gemm_bcast(h1_local[: r1 - r0], W2.contiguous(), [int(p) for p in hdl.buffer_ptrs], r0)
+                    self.gather_bytes += (self.n - (r1 - r0)) * W2.shape[1] * 2
+                mark("gemm2+exchange")
+                hdl.barrier(channel=1)                 # all rows of all ranks have landed
+                mark("barrier")
         else:
-            raise ValueError("gather must be 'h1', 'z2', 'fused' or 'push'")
+            raise ValueError("gather must be 'h1', 'z2', 'fused', 'push' or 'gemm_bcast'")
         out = self.plan.run(z2)[: r1 - r0] if r1 > r0 else z2[:0]
         mark("spmm2")
         if self.profile:
