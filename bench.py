@@ -751,7 +751,7 @@ def run_gcn(args, rank, world, local_rank):
     W1 = (torch.randn(256, 128, device=dev, generator=g) * 0.02).half()
     W2 = (torch.randn(128, 64, device=dev, generator=g) * 0.02).half()
     from trspmm import shard
-    cuts = shard.refined_cuts(rp, col, val, rank, world, 128, strict=args.strict) if world > 1 else None
+    cuts = shard.refined_cuts(rp, col, val, rank, world, (128, 64), strict=args.strict) if world > 1 else None
     model = ShardedGCN2(rp, col, val, rank, world, cuts=cuts, strict=args.strict)
     kept = model.stats["nnz"] - model.stats["dropped_nnz"]
     for _ in range(args.warmup):

@@ -36,3 +36,32 @@ def test_our_arm_has_no_cpu_fallback():
     r = _run("--workload", "uniform", "--steps", "1", "--warmup", "1")
     assert r.returncode != 0
     assert "CUDA" in (r.stderr + r.stdout)
+
+
+def test_kept_entry_mask_marks_exactly_the_dropped_entries():
+    """The checker of `bench.py --op gcn` recomputes the layer over the entries the built format
+    holds: its mask must zero exactly the entries the reference builder's 2-per-group rule drops
+    (block_online.cpp:683-695), so that mask-weighted CSR x B equals the product of the format."""
+    import importlib.util
+    sys.path.insert(0, str(ROOT / "tr-spmm_zzx_b200"))
+    sys.path.insert(0, str(ROOT))
+    from oracle import oracle as O
+    from trspmm import graphs
+    from trspmm.format import Format
+    spec = importlib.util.spec_from_file_location("bench_mod", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    rp, col, val = graphs.rmat_graph(10, 16, seed=2)
+    arrays, info = O.build_format(rp, col, val)
+    fmt = Format(arrays)
+    n = rp.numel() - 1
+    keep = bench.kept_entry_mask(rp, col, fmt, n)
+    assert keep.numel() == col.numel()
+    dropped = int((keep == 0).sum())
+    assert dropped == info["dropped_nnz"] and dropped > 0
+    # the product of the format (oracle forward over its three routes) equals the masked CSR product
+    B = torch.randn(n, 32, generator=torch.Generator().manual_seed(1)).half().float()
+    A = torch.sparse_csr_tensor(rp.long(), col.long(), val.half().float() * keep.float(), (n, n))
+    want = torch.sparse.mm(A, B)
+    got = O.spmm_from_format(arrays, B, n)
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-4)

@@ -58,7 +58,7 @@ def test_gcn2_two_ranks_match_single_rank():
     assert "GCN2 ranks agree" in r.stdout
 
 
-@pytest.mark.parametrize("rows,K,N", [(1000, 128, 64), (16, 16, 32), (4099, 256, 128), (33, 64, 64)])
+@pytest.mark.parametrize("rows,K,N", [(1000, 128, 64), (16, 32, 32), (4099, 256, 128), (33, 64, 64)])
 def test_rows_gemm_bcast_matches_a_dense_product(rows, K, N):
     """trs_rows_gemm_bcast with two destination buffers on one GPU: both get H @ W at the row offset,
     nothing else is touched."""
@@ -79,4 +79,17 @@ def test_rows_gemm_bcast_matches_a_dense_product(rows, K, N):
     with pytest.raises(Exception):
         rows_gemm_bcast(H, W, [], 0)
     with pytest.raises(Exception):
-        rows_gemm_bcast(H[:, :K - 8].contiguous(), W[:K - 8].contiguous(), [dsts[0].data_ptr()], 0)
+        rows_gemm_bcast(H[:, :K - 8].contiguous(), W[:K - 8].contiguous(), [dsts[0].data_ptr()], 0)   # K not a multiple of 16
+
+
+def test_rows_gemm_bcast_rejects_shapes_it_is_not_laid_out_for():
+    from trspmm.gcn import rows_gemm_bcast
+    from trspmm._lib import TrsError
+    H = torch.zeros(16, 16, dtype=torch.float16, device="cuda")
+    W = torch.zeros(16, 32, dtype=torch.float16, device="cuda")          # N > K
+    out = torch.zeros(16, 32, dtype=torch.float16, device="cuda")
+    with pytest.raises(TrsError):
+        rows_gemm_bcast(H, W, [out.data_ptr()], 0)
+    W48 = torch.zeros(16, 48, dtype=torch.float16, device="cuda")         # N not 32 / 64 / 128
+    with pytest.raises(TrsError):
+        rows_gemm_bcast(H, W48, [out.data_ptr()], 0)

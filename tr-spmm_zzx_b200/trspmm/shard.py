@@ -94,13 +94,14 @@ def shard_for_rank(rowptr, col, val, rank: int, world: int, window: int = 16):
     return (r0, r1), slice_csr(rowptr, col, val, r0, r1)
 
 
-def refined_cuts(rowptr, col, val, rank: int, world: int, F: int, strict: bool = False, rounds: int = 2,
+def refined_cuts(rowptr, col, val, rank: int, world: int, F, strict: bool = False, rounds: int = 2,
                  window: int = 16, group=None):
     """Row cuts balanced by what the ranks measure (a collective: every rank of `group` calls it with
     the whole matrix on its GPU).  First cut by nnz; re-cut by the k-steps the built format really
     has per window (hub windows share columns, so their cost per nnz is lower) plus a fixed
     per-window overhead; then up to `rounds` re-cuts from the kernel time each rank measures on its
-    own shard with an [n, F] operand (hub windows and L2 behaviour are not in the step count)."""
+    own shard with an [n, F] operand (hub windows and L2 behaviour are not in the step count).  F may
+    be a sequence of widths - the SpMMs of the layers of a model - whose times are added."""
     import torch.distributed as dist
     from .builder import build_format
     from .spmm import SpmmPlan
@@ -115,28 +116,32 @@ def refined_cuts(rowptr, col, val, rank: int, world: int, F: int, strict: bool =
     dist.all_reduce(cost, op=dist.ReduceOp.SUM, group=group)
     cuts = cuts_from_window_costs(cost, world, n, window)
     del fmt
-    Bt = torch.randn(n, F, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).half()
+    widths = (int(F),) if isinstance(F, int) else tuple(int(f) for f in F)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    Bts = [torch.randn(n, f, device=dev, generator=gen).half() for f in widths]
     for _ in range(rounds):
         r0, r1 = cuts[rank], cuts[rank + 1]
         rp_l, col_l, val_l = slice_csr(rowptr, col, val, r0, r1)
         fmt_t, _st = build_format(rp_l, col_l, val_l, window=window, strict=strict)
         plan_t = SpmmPlan(fmt_t, max(r1 - r0, 1), n, window, validate=False)
-        out_t = torch.empty((max(r1 - r0, 1), F), dtype=torch.float16, device=dev)
+        outs_t = [torch.empty((max(r1 - r0, 1), f), dtype=torch.float16, device=dev) for f in widths]
         for _i in range(3):
-            plan_t.run(Bt, out=out_t)
+            for Bt, out_t in zip(Bts, outs_t):
+                plan_t.run(Bt, out=out_t)
         torch.cuda.synchronize()
         dist.barrier(group=group)
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a0.record()
         for _i in range(5):
-            plan_t.run(Bt, out=out_t)
+            for Bt, out_t in zip(Bts, outs_t):
+                plan_t.run(Bt, out=out_t)
         a1.record()
         torch.cuda.synchronize()
         mine_t = torch.tensor([a0.elapsed_time(a1) / 5], device=dev)
         all_t = [torch.zeros_like(mine_t) for _i in range(world)]
         dist.all_gather(all_t, mine_t, group=group)
         times = [float(t) for t in all_t]
-        del plan_t, fmt_t, out_t
+        del plan_t, fmt_t, outs_t
         if max(times) <= 1.03 * (sum(times) / world):
             break
         cost = rescale_costs(cost, cuts, times, window)
