@@ -333,7 +333,8 @@ def run_ours(args, rank, world, local_rank):
         del rid
     if world > 1:
         # cut by nnz, re-cut by the k-steps of the built format, then by measured kernel time
-        cuts = shard.refined_cuts(rp, col, val, rank, world, F, strict=args.strict)
+        cut_report = {}
+        cuts = shard.refined_cuts(rp, col, val, rank, world, F, strict=args.strict, rounds=3, report=cut_report)
         r0, r1 = cuts[rank], cuts[rank + 1]
         rp_l, col_l, val_l = shard.slice_csr(rp, col, val, r0, r1)
     else:
@@ -489,7 +490,8 @@ def run_ours(args, rank, world, local_rank):
                        "nnz": nnz_total, "kept_nnz": int(kept_total), "F": F, "out": "f16",
                        "parallelism": f"row-window shards x{world} balanced by k-steps and measured kernel time, B replicated, no collective",
                        "l2": "inputs larger than L2 (no flush)" if n * F * 2 > 126e6 else "B fits L2",
-                       "build_ms_rank0": st["build_ms"], "tiles_rank0": st["tiles"], "tc_blocks_rank0": st["tc_blocks"]},
+                       "build_ms_rank0": st["build_ms"], "tiles_rank0": st["tiles"], "tc_blocks_rank0": st["tc_blocks"],
+                       "cut_refinement_kernel_ms_per_rank": cut_report.get("times_ms") if world > 1 else None},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "algorithmic_bytes_per_step_rank0": alg_rank,
                          "algorithmic_bytes_per_step_job": alg_job,
@@ -751,8 +753,11 @@ def run_gcn(args, rank, world, local_rank):
     W1 = (torch.randn(256, 128, device=dev, generator=g) * 0.02).half()
     W2 = (torch.randn(128, 64, device=dev, generator=g) * 0.02).half()
     from trspmm import shard
-    cuts = shard.refined_cuts(rp, col, val, rank, world, (128, 64), strict=args.strict) if world > 1 else None
+    cut_report = {}
+    cuts = (shard.refined_cuts(rp, col, val, rank, world, (128, 64), strict=args.strict, rounds=4, report=cut_report)
+            if world > 1 else None)
     model = ShardedGCN2(rp, col, val, rank, world, cuts=cuts, strict=args.strict)
+    model.multicast = not args.no_multicast
     kept = model.stats["nnz"] - model.stats["dropped_nnz"]
     for _ in range(args.warmup):
         model.forward(X, W1, W2, gather=args.gather)
@@ -812,11 +817,12 @@ def run_gcn(args, rank, world, local_rank):
                           "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                           "dtype": "f16 in / f32 accumulate", "data": "synthetic",
-                          "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather,
+                          "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather + ("+multicast" if (args.gather == "gemm_bcast" and world > 1 and not args.no_multicast) else ""),
                                      "n_rows": n, "nnz": nnz, "kept_nnz": int(kept_total),
                                      "format": "lossless (strict)" if args.strict else "reference-compatible (drops reproduced)",
                                      "gather_bytes_received_rank0": model.gather_bytes,
-                                     "stage_ms_rank0": breakdown},
+                                     "stage_ms_rank0": breakdown,
+                                     "cut_refinement_kernel_ms_per_rank": cut_report.get("times_ms")},
                           "parity_sample": {"max_row_normalised": p_max, "mean_rel": p_mean, "rows": n, "bars": [4e-3, 1e-3],
                                             "checker": "torch.sparse CSR fp32 two-layer forward over the entries the built "
                                                        "format holds, fp16 at the stage boundaries, every rank's own rows, "
@@ -842,7 +848,10 @@ def main():
                     help="spmm (default, the headline metric); sddmm and gcn are the other benchmark configurations")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "push"],
                     help="multi-GPU host-buffer path: how the ranks exchange their slices of B")
-    ap.add_argument("--gather", default="push", choices=["h1", "z2", "fused", "push", "gemm_bcast"], help="gcn: which matrix the ranks exchange")
+    ap.add_argument("--no-multicast", action="store_true",
+                    help="gcn, gather=gemm_bcast: one store per peer instead of one store through the NVLink multicast "
+                         "mapping (multimem.st), which is the default where the box offers one")
+    ap.add_argument("--gather", default="gemm_bcast", choices=["h1", "z2", "fused", "push", "gemm_bcast"], help="gcn: which matrix the ranks exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

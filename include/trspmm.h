@@ -127,6 +127,12 @@ int trs_spmm_run_bcast(const trs_spmm_plan* plan, const trs_half* B, void* const
  * to 256, N in {32, 64, 128}, N <= K, all pointers 16-byte aligned.  Asynchronous on `stream`. */
 int trs_rows_gemm_bcast(const trs_half* H, const trs_half* W, void* const* dst, int n_dst, long long row0,
                         int rows, int K, int N, void* stream);
+/* The same product with the rows stored once through an NVLink multicast address (multimem.st):
+ * `multicast_dst` is the multicast mapping of the [N_total, N] buffers of all ranks (e.g. the
+ * multicast_ptr of a torch symmetric-memory handle); the switch delivers every store to every bound
+ * GPU, this one included, so the sender issues each row once whatever the number of ranks. */
+int trs_rows_gemm_mcast(const trs_half* H, const trs_half* W, void* multicast_dst, long long row0, int rows,
+                        int K, int N, void* stream);
 /* Health word of the plan's kernels.  No kernel of the library waits on a flag or barrier another
  * warp or kernel sets, so there is no wait that could give up: always 0.  Kept for callers of
  * earlier versions. */

@@ -29,8 +29,18 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t& r0, u
 
 constexpr int kGemmWarps = 8;
 
-// NT = N / 8 (compile-time so that the accumulators stay in registers)
-template <int NT>
+// One 16-byte store through an NVLink multicast address: the switch delivers it to every GPU bound
+// to the multicast object (this one included), so the sender issues each row once instead of once
+// per peer.
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
+// NT = N / 8 (compile-time so that the accumulators stay in registers); MC: dst.ptr[0] is a
+// multicast address and takes the one store per row piece
+template <int NT, bool MC>
 __global__ void __launch_bounds__(kGemmWarps * 32) k_rows_gemm_bcast(const __half* __restrict__ H, const __half* __restrict__ W,
                                                                      RowDst dst, long long row0, int rows, int K) {
     constexpr int N = NT * 8;
@@ -88,7 +98,9 @@ __global__ void __launch_bounds__(kGemmWarps * 32) k_rows_gemm_bcast(const __hal
             if (r_base + r >= rows) continue;
             const uint4 v = *(const uint4*)(Hs + r * wpitch + ch * 16);
             const size_t off = (size_t)(row0 + r_base + r) * N + ch * 8;
-            for (int d = 0; d < dst.n; ++d) *(uint4*)((__half*)dst.ptr[d] + off) = v;
+            if (MC) multimem_st_16((__half*)dst.ptr[0] + off, v);
+            else
+                for (int d = 0; d < dst.n; ++d) *(uint4*)((__half*)dst.ptr[d] + off) = v;
         }
         __syncwarp();
     }
@@ -96,8 +108,8 @@ __global__ void __launch_bounds__(kGemmWarps * 32) k_rows_gemm_bcast(const __hal
 
 }  // namespace trs
 
-extern "C" int trs_rows_gemm_bcast(const trs_half* H, const trs_half* W, void* const* dst, int n_dst, long long row0,
-                                   int rows, int K, int N, void* stream) {
+static int rows_gemm_launch(const trs_half* H, const trs_half* W, void* const* dst, int n_dst, bool multicast,
+                            long long row0, int rows, int K, int N, void* stream) {
     using namespace trs;
     if (!H || !W || !dst || n_dst < 1 || n_dst > 8 || row0 < 0 || rows < 0) return TRS_E_ARG;
     if (K < 16 || K > 256 || K % 16 != 0) return TRS_E_ARG;
@@ -115,23 +127,32 @@ extern "C" int trs_rows_gemm_bcast(const trs_half* H, const trs_half* W, void* c
     cudaStream_t st = (cudaStream_t)stream;
     // the tile buffer is reused for the N-wide output rows: its rows must hold either
     const int hpitch = (K + 8) * 2, wpitch = (N + 8) * 2;
-    const int tile_bytes = 16 * (hpitch > wpitch ? hpitch : wpitch);
+    if (wpitch > hpitch) return TRS_E_ARG;   // N > K is not laid out for (not a GCN layer shape)
     const int smem = K * wpitch + kGemmWarps * 16 * hpitch;
-    if (tile_bytes > 16 * hpitch) return TRS_E_ARG;   // N > K is not laid out for (not a GCN layer shape)
     const int tiles = (rows + 15) / 16;
     int grid = (tiles + kGemmWarps - 1) / kGemmWarps;
     if (grid > 148 * 3) grid = 148 * 3;
     const __half *h = (const __half*)H, *w = (const __half*)W;
-    if (N == 32) {
-        TRS_CUDA(cudaFuncSetAttribute(k_rows_gemm_bcast<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        k_rows_gemm_bcast<4><<<grid, kGemmWarps * 32, smem, st>>>(h, w, rd, row0, rows, K);
-    } else if (N == 64) {
-        TRS_CUDA(cudaFuncSetAttribute(k_rows_gemm_bcast<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        k_rows_gemm_bcast<8><<<grid, kGemmWarps * 32, smem, st>>>(h, w, rd, row0, rows, K);
-    } else {
-        TRS_CUDA(cudaFuncSetAttribute(k_rows_gemm_bcast<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        k_rows_gemm_bcast<16><<<grid, kGemmWarps * 32, smem, st>>>(h, w, rd, row0, rows, K);
-    }
+    auto launch = [&](auto kernel) -> int {
+        TRS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kernel<<<grid, kGemmWarps * 32, smem, st>>>(h, w, rd, row0, rows, K);
+        return TRS_OK;
+    };
+    int rc;
+    if (multicast) rc = N == 32 ? launch(k_rows_gemm_bcast<4, true>) : N == 64 ? launch(k_rows_gemm_bcast<8, true>) : launch(k_rows_gemm_bcast<16, true>);
+    else rc = N == 32 ? launch(k_rows_gemm_bcast<4, false>) : N == 64 ? launch(k_rows_gemm_bcast<8, false>) : launch(k_rows_gemm_bcast<16, false>);
+    if (rc) return rc;
     TRS_LAUNCH_CHECK();
     return TRS_OK;
+}
+
+extern "C" int trs_rows_gemm_bcast(const trs_half* H, const trs_half* W, void* const* dst, int n_dst, long long row0,
+                                   int rows, int K, int N, void* stream) {
+    return rows_gemm_launch(H, W, dst, n_dst, false, row0, rows, K, N, stream);
+}
+
+extern "C" int trs_rows_gemm_mcast(const trs_half* H, const trs_half* W, void* multicast_dst, long long row0, int rows,
+                                   int K, int N, void* stream) {
+    void* d[1] = {multicast_dst};
+    return rows_gemm_launch(H, W, d, 1, true, row0, rows, K, N, stream);
 }

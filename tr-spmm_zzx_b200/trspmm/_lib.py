@@ -81,6 +81,8 @@ def load():
     lib.trs_spmm_run_bcast.restype = i32
     lib.trs_rows_gemm_bcast.argtypes = [vp, vp, C.POINTER(vp), i32, C.c_longlong, i32, i32, i32, vp]
     lib.trs_rows_gemm_bcast.restype = i32
+    lib.trs_rows_gemm_mcast.argtypes = [vp, vp, vp, C.c_longlong, i32, i32, i32, vp]
+    lib.trs_rows_gemm_mcast.restype = i32
     lib.trs_spmm_run_static.argtypes = [vp, vp, vp, i32, i32, vp]
     lib.trs_spmm_run_static.restype = i32
     lib.trs_spmm_static_scratch_bytes.argtypes = [vp, i32, C.POINTER(sz)]

@@ -17,10 +17,11 @@ from .builder import build_format
 from .spmm import SpmmPlan
 
 
-def rows_gemm_bcast(H: torch.Tensor, W: torch.Tensor, dst_ptrs, row0: int):
+def rows_gemm_bcast(H: torch.Tensor, W: torch.Tensor, dst_ptrs, row0: int, multicast_ptr: int = 0):
     """trs_rows_gemm_bcast: Z[row0 + r] = H[r] @ W, the fp16 rows written by the one kernel into every
     buffer of `dst_ptrs` (device pointers of [N_total, N] fp16 matrices: this GPU's and its NVLink
-    peers').  Asynchronous on the current stream."""
+    peers').  With `multicast_ptr` (the NVLink multicast mapping of those buffers) the rows are stored
+    once through it instead (trs_rows_gemm_mcast).  Asynchronous on the current stream."""
     import ctypes as C
     from . import _lib
     if H.dtype != torch.float16 or W.dtype != torch.float16 or not H.is_cuda or H.device != W.device:
@@ -30,6 +31,11 @@ def rows_gemm_bcast(H: torch.Tensor, W: torch.Tensor, dst_ptrs, row0: int):
     if not 1 <= len(dst_ptrs) <= 8 or row0 < 0:
         raise ValueError("1 to 8 destination buffers and a non-negative row offset")
     lib = _lib.load()
+    if multicast_ptr:
+        with torch.cuda.device(H.device):
+            _lib.check(lib.trs_rows_gemm_mcast(H.data_ptr(), W.data_ptr(), int(multicast_ptr), int(row0), H.shape[0],
+                                               H.shape[1], W.shape[1], _lib.current_stream_ptr(H.device)))
+        return
     arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
     with torch.cuda.device(H.device):
         _lib.check(lib.trs_rows_gemm_bcast(H.data_ptr(), W.data_ptr(), arr, len(dst_ptrs), int(row0), H.shape[0],
@@ -52,16 +58,20 @@ class ShardedGCN2:
         self._symm = {}   # feature width -> (tensor, handle) of the peer-mapped hidden matrix
         self._copy_streams = None
         self.push_chunks = 2
+        self._calls = 0
+        self.multicast = True    # gemm_bcast: store through the NVLink multicast mapping when the handle has one
 
-    def _symmetric(self, F: int, device):
-        """A [N, F] fp16 matrix every rank of the box can store into (torch symmetric memory)."""
-        if F not in self._symm:
+    def _symmetric(self, F, device):
+        """A [N, F] fp16 matrix every rank of the box can store into (torch symmetric memory).  F may be
+        a (width, slot) pair: one buffer per slot."""
+        key, F = F, (F[0] if isinstance(F, tuple) else F)
+        if key not in self._symm:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm_mem
             t = symm_mem.empty((self.n, F), dtype=torch.float16, device=device)
             hdl = symm_mem.rendezvous(t, group=self.group if self.group is not None else dist.group.WORLD)
-            self._symm[F] = (t, hdl)
-        return self._symm[F]
+            self._symm[key] = (t, hdl)
+        return self._symm[key]
 
     def _exchange(self, full: torch.Tensor):
         """Every rank's rows [cuts[r], cuts[r+1]) of `full` become valid on all ranks.  The blocks
@@ -194,12 +204,18 @@ class ShardedGCN2:
                 rows_gemm_bcast(h1_local[: r1 - r0].contiguous(), W2.contiguous(), [z2.data_ptr()], r0)
                 mark("spmm1+gemm2")
             else:
-                z2, hdl = self._symmetric(W2.shape[1], X.device)
-                hdl.barrier(channel=0)                 # every rank is done reading the previous Z2
+                # two Z2 buffers used in turn: a rank that runs ahead writes the other buffer, and it cannot
+                # get two calls ahead, because the barrier below needs every rank's previous call finished -
+                # so one barrier per call is enough (none before the stores)
+                self._calls += 1
+                z2, hdl = self._symmetric((W2.shape[1], self._calls & 1), X.device)
                 if r1 > r0:
                     h1_local = self.plan.run(z1, relu=True)
                     mark("spmm1")
-                    rows_gemm_bcast(h1_local[: r1 - r0], W2.contiguous(), [int(p) for p in hdl.buffer_ptrs], r0)
+                    # (the SpMM in window chunks with the GEMM + stores of a finished chunk on a second stream
+                    # was measured on four ranks: 1.06 / 1.33 ms with two / four chunks against 0.82 ms)
+                    mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.multicast else 0
+                    rows_gemm_bcast(h1_local[: r1 - r0], W2.contiguous(), [int(p) for p in hdl.buffer_ptrs], r0, mc)
                     self.gather_bytes += (self.n - (r1 - r0)) * W2.shape[1] * 2
                 mark("gemm2+exchange")
                 hdl.barrier(channel=1)                 # all rows of all ranks have landed

@@ -95,13 +95,15 @@ def shard_for_rank(rowptr, col, val, rank: int, world: int, window: int = 16):
 
 
 def refined_cuts(rowptr, col, val, rank: int, world: int, F, strict: bool = False, rounds: int = 2,
-                 window: int = 16, group=None):
+                 window: int = 16, group=None, report: dict = None):
     """Row cuts balanced by what the ranks measure (a collective: every rank of `group` calls it with
     the whole matrix on its GPU).  First cut by nnz; re-cut by the k-steps the built format really
     has per window (hub windows share columns, so their cost per nnz is lower) plus a fixed
     per-window overhead; then up to `rounds` re-cuts from the kernel time each rank measures on its
     own shard with an [n, F] operand (hub windows and L2 behaviour are not in the step count).  F may
-    be a sequence of widths - the SpMMs of the layers of a model - whose times are added."""
+    be a sequence of widths - the SpMMs of the layers of a model - whose times are added.  `report`,
+    when given, receives the per-rank times of every round ("times_ms": list of lists; the last
+    list belongs to the cut before the returned one unless the loop stopped on balance)."""
     import torch.distributed as dist
     from .builder import build_format
     from .spmm import SpmmPlan
@@ -141,6 +143,8 @@ def refined_cuts(rowptr, col, val, rank: int, world: int, F, strict: bool = Fals
         all_t = [torch.zeros_like(mine_t) for _i in range(world)]
         dist.all_gather(all_t, mine_t, group=group)
         times = [float(t) for t in all_t]
+        if report is not None:
+            report.setdefault("times_ms", []).append([round(t, 4) for t in times])
         del plan_t, fmt_t, outs_t
         if max(times) <= 1.03 * (sum(times) / world):
             break

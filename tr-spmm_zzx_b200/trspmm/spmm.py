@@ -52,7 +52,8 @@ class SpmmPlan:
         return n.value
 
     def status(self) -> int:
-        """0, or non-zero when a bounded wait inside a kernel gave up (synchronises the device)."""
+        """Health word of the plan's kernels (trs_spmm_status): always 0 - no kernel of the library waits on
+        a flag another warp or kernel sets, so no wait can give up.  Kept for callers of earlier versions."""
         v = C.c_int()
         _lib.check(self.lib.trs_spmm_status(self._handle, C.byref(v)))
         return v.value
