@@ -817,7 +817,7 @@ def run_gcn(args, rank, world, local_rank):
                           "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
                           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                           "dtype": "f16 in / f32 accumulate", "data": "synthetic",
-                          "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather + ("+multicast" if (args.gather == "gemm_bcast" and world > 1 and not args.no_multicast) else ""),
+                          "config": {"workload": args.workload, "op": "gcn2", "features": [256, 128, 64], "gather": args.gather + ("+multicast" if (args.gather == "gemm_bcast" and world > 2 and not args.no_multicast) else ""),
                                      "n_rows": n, "nnz": nnz, "kept_nnz": int(kept_total),
                                      "format": "lossless (strict)" if args.strict else "reference-compatible (drops reproduced)",
                                      "gather_bytes_received_rank0": model.gather_bytes,

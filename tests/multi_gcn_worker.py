@@ -46,7 +46,7 @@ def main():
     for _ in range(3):
         ok = ok and bool(torch.equal(model.forward(X, W1, W2, gather="gemm_bcast"), one))
     # ... and with the rows stored once through the NVLink multicast mapping, where the box offers one
-    model.multicast = True
+    model.multicast, model.multicast_min_world = True, 2      # (by default the model takes this path from three ranks on)
     for _ in range(2):
         ok = ok and bool(torch.equal(model.forward(X, W1, W2, gather="gemm_bcast"), one))
     flag = torch.tensor([1 if ok else 0], device=dev)

@@ -59,7 +59,8 @@ class ShardedGCN2:
         self._copy_streams = None
         self.push_chunks = 2
         self._calls = 0
-        self.multicast = True    # gemm_bcast: store through the NVLink multicast mapping when the handle has one
+        self.multicast = True    # gemm_bcast: store through the NVLink multicast mapping when the handle has one,
+        self.multicast_min_world = 3   # from this many ranks on
 
     def _symmetric(self, F, device):
         """A [N, F] fp16 matrix every rank of the box can store into (torch symmetric memory).  F may be
@@ -214,7 +215,9 @@ class ShardedGCN2:
                     mark("spmm1")
                     # (the SpMM in window chunks with the GEMM + stores of a finished chunk on a second stream
                     # was measured on four ranks: 1.06 / 1.33 ms with two / four chunks against 0.82 ms)
-                    mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.multicast else 0
+                    # with one peer a plain store already sends every row once (2 ranks measured 0.99 ms
+                    # with it, 1.06 ms through the multicast mapping; 4 ranks 0.83 against 0.75 ms)
+                    mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if (self.multicast and self.world >= self.multicast_min_world) else 0
                     rows_gemm_bcast(h1_local[: r1 - r0], W2.contiguous(), [int(p) for p in hdl.buffer_ptrs], r0, mc)
                     self.gather_bytes += (self.n - (r1 - r0)) * W2.shape[1] * 2
                 mark("gemm2+exchange")
