@@ -910,16 +910,10 @@ extern "C" int trs_spmm_plan_create(const trs_format* dev_format, int m_rows, in
     p->f = f;
     p->m_rows = m_rows; p->k_cols = k_cols; p->window = window; p->num_windows = W;
     // Longest run of k-steps one warp takes (longer windows are split into several items that write
-    // partial sums).  256 for a matrix that fills the GPU many times over; a shard with fewer steps
-    // gets shorter items, so that the kernel's duration is not set by its longest item (a row-window
-    // shard of R-MAT scale 20 on 8 GPUs took 0.2 ms however few windows it had: 256 steps of ~1 us).
-    {
-        const long long total_steps = (long long)f.tiles + (f.blocks + 1) / 2;
-        const long long resident = 148LL * 16 * 4;        // four waves of one-warp items
-        long long c = (total_steps / resident + 7) / 8 * 8;
-        c = c < 64 ? 64 : c > 256 ? 256 : c;
-        p->chunk = max(8, env_int("TRS_CHUNK_STEPS", (int)c));
-    }
+    // partial sums).  Shorter items for small shards (64 to 256 by the shard's number of steps) were
+    // measured and not kept: R-MAT scale 20 on one GPU 0.83 against 0.81 ms, a four-rank shard 0.46
+    // against 0.42 ms - the extra partial sums cost more than the shorter critical path wins.
+    p->chunk = max(8, env_int("TRS_CHUNK_STEPS", 256));
     // per-window ranges of TC blocks and CSR parts (needed only while the items are made)
     DevBuf<int> ranges, cnt, off;
     DevBuf<unsigned char> tmp;
