@@ -200,9 +200,10 @@ class ShardedGCN2:
                 mark("barrier")
         elif gather == "gemm_bcast":
             if self.world == 1:
+                # nothing to exchange: a plain library GEMM (0.073 ms for 2^20 rows; the fused kernel with
+                # its single destination takes 0.10 ms)
                 h1_local = self.plan.run(z1, relu=True)
-                z2 = torch.empty((self.n, W2.shape[1]), dtype=torch.float16, device=X.device)
-                rows_gemm_bcast(h1_local[: r1 - r0].contiguous(), W2.contiguous(), [z2.data_ptr()], r0)
+                z2 = torch.matmul(h1_local[: r1 - r0], W2)
                 mark("spmm1+gemm2")
             else:
                 # two Z2 buffers used in turn: a rank that runs ahead writes the other buffer, and it cannot
