@@ -210,7 +210,7 @@ __global__ void k_item_class(const Item* __restrict__ items, int n, unsigned cha
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int steps = items[i].step_end - items[i].step_begin + items[i].ce_n;
-    cls[i] = (unsigned char)(31 - min(steps, 255) / 8);   // 32 classes of 8 steps (four classes measured 4 - 6 % slower)
+    cls[i] = (unsigned char)(31 - min(steps, 255) / 8);   // 32 classes of 8 steps (four classes measured 4 - 6 % slower, 64 or 256 the same)
 }
 
 // The TC kernels read t_value[t_block_offset[b] + rank] with rank taken from the block's two
